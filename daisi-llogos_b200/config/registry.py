@@ -139,3 +139,7 @@ register_architecture(_karitar.NAME, _karitar.KaritarConfig.from_dict, _karitar.
 from . import fipavik as _fipavik  # noqa: E402
 
 register_architecture(_fipavik.NAME, _fipavik.FipavikConfig.from_dict, _fipavik.fipavik_spec)
+
+from . import rukedra as _rukedra  # noqa: E402
+
+register_architecture(_rukedra.NAME, _rukedra.RukedraConfig.from_dict, _rukedra.rukedra_spec)

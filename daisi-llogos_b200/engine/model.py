@@ -25,6 +25,8 @@ from ..parts import latent_attention as _latent_attention  # noqa: F401
 from ..parts import moe as _moe  # noqa: F401
 from ..parts import norm as _norm  # noqa: F401
 from ..parts import position as _position  # noqa: F401
+from ..parts import recurrent as _recurrent  # noqa: F401
+from ..parts import sandwich as _sandwich  # noqa: F401
 
 
 class DecoderModel:

@@ -117,8 +117,10 @@ def gated_layout(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out.view(2 * pad, hidden)
 
 
-def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor, row_scale=None) -> None:
-    """out[n, i] = silu(x . gate_i) * (x . up_i) for a gate/up matrix in ``gated_layout``.
+def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor, row_scale=None,
+                 activation: str = "silu") -> None:
+    """out[n, i] = act(x . gate_i) * (x . up_i) for a gate/up matrix in ``gated_layout``; ``activation`` is "silu" or
+    "gelu_tanh" (one of ``ops.GATE_ACTIVATIONS``).
 
     On the tensor cores the gating is the epilogue of the product; otherwise the product writes
     gate and up values and the gating kernel follows.  ``row_scale`` as in ``linear``: both products' rows are
@@ -127,11 +129,12 @@ def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor,
     n = x.shape[0]
     rows = w_gated.shape[0]
     tc = getattr(ops, "gemm_tc_supported", None)
+    kw = {} if activation == "silu" else {"gate_activation": activation}      # the stock form's calls stay as they were
     if tc is not None and tc(x, w_gated) and out.dtype == torch.bfloat16:
         if row_scale is not None:
-            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1], row_scale=row_scale)
+            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1], row_scale=row_scale, **kw)
         else:
-            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1])
+            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1], **kw)
         return
     for r0 in range(0, n, _GATED_CHUNK):
         r1 = min(n, r0 + _GATED_CHUNK)
@@ -140,4 +143,4 @@ def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor,
             ops.gemm_simt(x[r0:r1], w_gated, gu[0], row_scale=row_scale.slice(r0, r1))
         else:
             ops.gemm_simt(x[r0:r1], w_gated, gu[0])
-        ops.silu_mul(gu, out[r0:r1])
+        ops.silu_mul(gu, out[r0:r1], **({} if activation == "silu" else {"activation": activation}))

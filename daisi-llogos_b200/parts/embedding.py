@@ -41,7 +41,8 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: vocab_size, hidden_size, tied_to (full name of the tensor to share, or None)."""
+    """params: vocab_size, hidden_size, tied_to (full name of the tensor to share, or None), softcap (0 or None: none;
+    c: the logits become ``c tanh(logits / c)``)."""
 
     TAKES_ROW_SCALE = True
 
@@ -50,6 +51,9 @@ class LinearHead(Part):
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.tied_to = params.get("tied_to")
+        self.softcap = float(params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError(f"output head: softcap must not be negative, got {self.softcap}")
         self.weight = None
 
     def tensors(self):
@@ -65,7 +69,10 @@ class LinearHead(Part):
 
     def forward(self, x, ctx, row_scale=None) -> torch.Tensor:
         # the logits go to samplers and callers as they are: one product, no partial sums to add up
-        return linear(ctx, x, self.weight, "head.logits", torch.float32, split_k=False, row_scale=row_scale)[0]
+        logits = linear(ctx, x, self.weight, "head.logits", torch.float32, split_k=False, row_scale=row_scale)[0]
+        if self.softcap:
+            ctx.ops.tanh_cap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

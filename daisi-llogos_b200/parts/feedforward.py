@@ -14,7 +14,8 @@ from .base import Branch, FeedForward, TensorDecl, register_part
 
 
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size."""
+    """``down(act(gate(x)) * up(x))``.  params: hidden_size, intermediate_size, activation (of the gate: one of
+    ``ops.GATE_ACTIVATIONS``, "silu" by default, or "gelu_tanh")."""
 
     TAKES_ROW_SCALE = True
 
@@ -22,6 +23,10 @@ class SwiGLU(FeedForward):
         super().__init__(params, prefix, env)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        known = getattr(env.ops, "GATE_ACTIVATIONS", ("silu",))
+        if self.activation not in known:
+            raise ValueError(f"swiglu: gate activation '{self.activation}' is not known ({', '.join(known)})")
         self.w_gate_up = None
         self.w_down = None
 
@@ -41,7 +46,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx, row_scale=None) -> Branch:
         act = ctx.buffer("ffn.act", (x.shape[0], self.inter))
-        gated_linear(ctx, x, self.w_gate_up, act, row_scale)
+        gated_linear(ctx, x, self.w_gate_up, act, row_scale, self.activation)
         return Branch(linear(ctx, act, self.w_down, "ffn.out", torch.float32))
 
 

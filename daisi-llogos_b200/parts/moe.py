@@ -1,9 +1,13 @@
 """A feed-forward of many small experts of which every token uses a few, beside an optional shared expert.
 
 Router: ``z = W_r h + b`` with float32 sums; the ``top`` experts of largest ``z`` are chosen per token and weighted by a
-softmax over the chosen logits alone.  Every expert is the gated form ``W_down (silu(W_gate h) * W_up h)`` without
+softmax over the chosen logits alone.  Or, by parameter (``score = "sigmoid"``): every expert's score is ``s = sigmoid(z)``; the
+experts form ``groups`` equal groups of neighbours, a group is judged by the sum of its ``group_score_top`` largest scores,
+and only the experts of the ``keep_groups`` best groups can be chosen; the ``top`` eligible experts of largest score are
+weighted by ``s / (sum of the chosen s + weight_sum_eps) * weight_scale``.  Every expert is the gated form ``W_down (silu(W_gate h) * W_up h)`` without
 biases; the token's output is the weighted sum of its experts' outputs, plus the shared expert's (which every token
-runs) where the layer has one.
+runs) where the layer has one; with ``shared_gate`` the shared expert's output is multiplied by ``sigmoid(w_sg . h)``, one
+number per token, whose row ``w_sg`` rides in the router's product.
 
 On the device the step's (token, choice) pairs are put in the order of their experts, every expert's run of rows
 filled up to a whole tile (``ops.moe_plan``), so that two grouped products (gate/up with the gating as its epilogue,
@@ -23,7 +27,9 @@ from .base import Branch, FeedForward, TensorDecl, as_f32, part_class, register_
 class MoeFeedForward(FeedForward):
     """params: hidden_size, num_experts, top, expert_size (an expert's inner size), shared_size (0 or None: no shared
     expert), router_bias (bool), shared_prefix (where the shared expert's tensors lie under this part's prefix,
-    default "shared."), shared_names (its ``tensor_names``).  Tensors: ``router.weight`` [experts, hidden],
+    default "shared."), shared_names (its ``tensor_names``), score ("softmax", the default, or "sigmoid"), groups and
+    keep_groups (0: every expert is eligible), group_score_top (default 2), weight_scale (default 1), weight_sum_eps
+    (default 0), shared_gate (bool: a tensor ``shared_gate.weight`` [1, hidden]).  Tensors: ``router.weight`` [experts, hidden],
     ``router.bias`` [experts], and per expert i ``experts.<i>.{gate_proj,up_proj,down_proj}.weight``."""
 
     def __init__(self, params, prefix, env):
@@ -42,6 +48,23 @@ class MoeFeedForward(FeedForward):
         if top_limit is not None and self.top > top_limit:
             raise ValueError(f"moe: top {self.top}; the routing kernels take up to {top_limit}")
         self.router_bias = bool(p.get("router_bias", False))
+        self.score = str(p.get("score", "softmax"))
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"moe: score '{self.score}' is not known (softmax, sigmoid)")
+        self.groups, self.keep_groups = int(p.get("groups") or 0), int(p.get("keep_groups") or 0)
+        if self.groups:
+            if self.score != "sigmoid":
+                raise ValueError("moe: groups of experts go with sigmoid scores")
+            if self.n_exp % self.groups or not 0 < self.keep_groups <= self.groups:
+                raise ValueError(f"moe: {self.n_exp} experts in {self.groups} groups of which {self.keep_groups} are kept")
+            if self.top > self.keep_groups * (self.n_exp // self.groups):
+                raise ValueError(f"moe: top {self.top} exceeds the experts of {self.keep_groups} groups")
+        self.group_score_top = int(p.get("group_score_top", 2))
+        self.weight_scale = float(p.get("weight_scale", 1.0))
+        self.weight_sum_eps = float(p.get("weight_sum_eps", 0.0))
+        self.shared_gate = bool(p.get("shared_gate", False))
+        if self.shared_gate and not int(p.get("shared_size") or 0):
+            raise ValueError("moe: a shared gate needs a shared expert")
         self.shared = None
         shared = int(p.get("shared_size") or 0)
         if shared:
@@ -72,6 +95,8 @@ class MoeFeedForward(FeedForward):
         t = {"router.weight": TensorDecl((self.n_exp, self.hidden))}
         if self.router_bias:
             t["router.bias"] = TensorDecl((self.n_exp,), "bias")
+        if self.shared_gate:
+            t["shared_gate.weight"] = TensorDecl((1, self.hidden))
         for i in range(self.n_exp):
             t[self._expert(i, "gate")] = TensorDecl((self.inter, self.hidden))
             t[self._expert(i, "up")] = TensorDecl((self.inter, self.hidden))
@@ -84,8 +109,14 @@ class MoeFeedForward(FeedForward):
     def bind(self, tensors):
         # A router stored in the compute type goes through the matrix product every other projection takes (the products
         # of bfloat16 values are exact in float32 and are added in float32); one stored wider keeps its own kernel.
-        self.w_router_same = tensors["router.weight"] if tensors["router.weight"].dtype == self.env.dtype else None
-        self.w_router = as_f32(tensors["router.weight"], self.env) if self.w_router_same is None else None
+        w_r = tensors["router.weight"]
+        if self.shared_gate:
+            # the shared expert's gate is one more row of the router's product
+            if tensors["shared_gate.weight"].dtype != w_r.dtype:
+                raise ValueError(f"{self.prefix}: the router and the shared expert's gate are stored with different types")
+            w_r = torch.cat([w_r, tensors["shared_gate.weight"].view(1, self.hidden)], dim=0).contiguous()
+        self.w_router_same = w_r if w_r.dtype == self.env.dtype else None
+        self.w_router = as_f32(w_r, self.env) if self.w_router_same is None else None
         self.b_router = as_f32(tensors["router.bias"], self.env) if self.router_bias else None
         per = {what: [tensors[self._expert(i, what)] for i in range(self.n_exp)] for what in ("gate", "up", "down")}
         if len({w.dtype for ws in per.values() for w in ws}) != 1:
@@ -108,12 +139,16 @@ class MoeFeedForward(FeedForward):
         pairs = n * self.top
         choice = ctx.buffer("moe.choice", (n, self.top), torch.int32)
         weight = ctx.buffer("moe.weight", (n, self.top), torch.float32)
+        plain = self.score == "softmax" and not self.shared_gate
+        shared_scale = ctx.buffer("moe.shared_scale", (n,), torch.float32) if self.shared_gate else None
+        rule = {} if plain else dict(rule=ops.RouterRule(self.score, self.groups, self.keep_groups, self.group_score_top,
+                                                        self.weight_scale, self.weight_sum_eps), extra_out=shared_scale)
         if self.w_router_same is not None and x.dtype == self.w_router_same.dtype and hasattr(ops, "moe_topk"):
-            ops.moe_topk(linear(ctx, x, self.w_router_same, "moe.logits", torch.float32), self.b_router, choice, weight)
+            ops.moe_topk(linear(ctx, x, self.w_router_same, "moe.logits", torch.float32), self.b_router, choice, weight, **rule)
         else:
             if self.w_router is None:
                 self.w_router = as_f32(self.w_router_same, self.env)
-            ops.moe_route(x, self.w_router, self.b_router, choice, weight)
+            ops.moe_route(x, self.w_router, self.b_router, choice, weight, **rule)
         tile = ops.moe_tile_rows(x.dtype, pairs, self.n_exp, self.hidden, self.inter)
         cap = ops.moe_row_capacity(pairs, self.n_exp, tile)
         row_of_pair = ctx.buffer("moe.row_of_pair", (pairs,), torch.int32)
@@ -132,7 +167,10 @@ class MoeFeedForward(FeedForward):
         ops.moe_down(act, tile_expert, self.w_down, y)
         shared = self.shared.forward(x, ctx).data if self.shared is not None else None
         out = ctx.buffer("moe.out", (1, n, self.hidden), torch.float32)
-        ops.moe_combine(y, row_of_pair, weight, shared, out[0])
+        if shared_scale is not None:
+            ops.moe_combine(y, row_of_pair, weight, shared, out[0], shared_scale=shared_scale)
+        else:
+            ops.moe_combine(y, row_of_pair, weight, shared, out[0])
         return Branch(out)
 
 

@@ -28,8 +28,21 @@ class Rotation:
     pairing: int             # 0 = half, 1 = adjacent
 
 
+def rotary_amplitude(scaling: Optional[dict]) -> float:
+    """What cos and sin are multiplied by: 1, or for yarn scaling ``amplitude_slope * ln(factor) + 1``."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return float(scaling.get("amplitude_slope", 0.1)) * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 def rotary_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
-    """float64 ``[rotary_dim / 2]``; ``scaling`` is a llama3 ``rope_scaling`` dict or None.
+    """float64 ``[rotary_dim / 2]``; ``scaling`` is a llama3 or yarn ``rope_scaling`` dict or None.
+
+    yarn: pair i makes ``t_i = L f_i / (2 pi)`` turns over the original context ``L``; the pair index at which a
+    frequency makes ``t`` turns is ``d(t) = rotary_dim ln(L / (2 pi t)) / (2 ln theta)``.  With ``lo = max(floor(d(beta_fast)),
+    0)`` and ``hi = min(ceil(d(beta_slow)), rotary_dim - 1)`` the ramp ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``
+    blends ``f' = r f / factor + (1 - r) f``: fast pairs keep their frequency, slow ones are stretched by ``factor``.
+    (The amplitude that goes with it is ``rotary_amplitude``.)
 
     llama3: with wavelength ``lam = 2 pi / f`` and ``L`` the original context length,
     ``f`` is kept where ``lam < L / high_freq_factor``, divided by ``factor`` where
@@ -39,6 +52,17 @@ def rotary_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
     half = rotary_dim // 2
     i = torch.arange(half, dtype=torch.float64)
     inv = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float64), 2.0 * i / rotary_dim)
+    if scaling and scaling.get("rope_type") == "yarn":
+        factor = float(scaling["factor"])
+        orig = float(scaling["original_max_position_embeddings"])
+
+        def pair_of(turns: float) -> float:
+            return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+        lo = max(math.floor(pair_of(float(scaling["beta_fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["beta_slow"]))), rotary_dim - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return inv / factor * ramp + inv * (1.0 - ramp)
     if scaling:
         if scaling.get("rope_type") != "llama3":
             raise ValueError(f"rotary scaling '{scaling.get('rope_type')}' is not supported")
@@ -79,8 +103,9 @@ class RotaryEncoding(PositionEncoding):
         inv = rotary_inverse_frequencies(self.rotary_dim, self.params["theta"], self.params.get("scaling"))
         pos = torch.arange(max_positions, dtype=torch.float64)
         ang = pos[:, None] * inv[None, :]
-        cos = torch.cos(ang).to(torch.float32).to(self.env.device).contiguous()
-        sin = torch.sin(ang).to(torch.float32).to(self.env.device).contiguous()
+        amp = rotary_amplitude(self.params.get("scaling"))
+        cos = (amp * torch.cos(ang)).to(torch.float32).to(self.env.device).contiguous()
+        sin = (amp * torch.sin(ang)).to(torch.float32).to(self.env.device).contiguous()
         self._rotation = Rotation(cos, sin, self.rotary_dim, self.pairing)
 
     def rotation(self) -> Rotation:

@@ -119,34 +119,103 @@ def add_layernorm(residual, parts, scale, weight, bias, eps, out, rows=None):
     out.copy_(((x - mu) * torch.rsqrt(var + eps) * weight.float() + bias.float()).to(out.dtype))
 
 
-def latent_prep(rows, *, n_heads, head_dim, rot_dim, kv_rank, c_norm_w, norm_eps, cos, sin, positions, q_plain_out, q_out,
-                k_new=None, v_new=None, k_pages=None, v_pages=None, page_table=None, ring_pages=0, seq_of_token=None,
-                slots=None):
+def latent_prep(rows, *, n_heads, head_dim, rot_dim, kv_rank, c_norm_w, norm_eps, cos, sin, positions, q_plain_out=None,
+                q_out=None, k_new=None, v_new=None, k_pages=None, v_pages=None, page_table=None, ring_pages=0, seq_of_token=None,
+                slots=None, pairing=0, q_col=0, kv_col=None, cq_col=-1, cq_norm_w=None, cq_out=None):
     x = rows.float().sum(0)
     n = x.shape[0]
     qw = n_heads * (head_dim + rot_dim)
-    q = x[:, :qw].view(n, n_heads, head_dim + rot_dim)
-    c = x[:, qw:qw + kv_rank]
-    kr = x[:, qw + kv_rank:]
-    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + norm_eps) * c_norm_w.float()
+    if kv_col is None:
+        kv_col = qw
 
     def rotate(t):                      # [..., rot_dim] with a leading token axis
         half = rot_dim // 2
         cs, sn = cos[positions.long()], sin[positions.long()]
         while cs.dim() < t.dim():
             cs, sn = cs.unsqueeze(1), sn.unsqueeze(1)
-        a, b = t[..., :half], t[..., half:]
-        return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1)
+        if pairing == 0:
+            a, b = t[..., :half], t[..., half:]
+            return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1)
+        a, b = t[..., 0::2], t[..., 1::2]
+        return torch.stack([a * cs - b * sn, b * cs + a * sn], dim=-1).flatten(-2)
 
-    q_plain_out.copy_(q[..., :head_dim].to(q_plain_out.dtype))
+    if cq_col >= 0:
+        cq = x[:, cq_col:cq_col + cq_out.shape[1]]
+        cq_out.copy_((cq * torch.rsqrt((cq * cq).mean(-1, keepdim=True) + norm_eps) * cq_norm_w.float()).to(cq_out.dtype))
+    if q_col >= 0:
+        q = x[:, q_col:q_col + qw].view(n, n_heads, head_dim + rot_dim)
+        q_plain_out.copy_(q[..., :head_dim].to(q_plain_out.dtype))
+        if rot_dim:
+            q_out[..., kv_rank:] = rotate(q[..., head_dim:]).to(q_out.dtype)
+    if kv_col < 0:
+        return
+    c = x[:, kv_col:kv_col + kv_rank]
+    kr = x[:, kv_col + kv_rank:kv_col + kv_rank + rot_dim]
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + norm_eps) * c_norm_w.float()
     if rot_dim:
-        q_out[..., kv_rank:] = rotate(q[..., head_dim:]).to(q_out.dtype)
         kr = rotate(kr)
-    k = torch.cat([c, kr], dim=-1).view(n, 1, kv_rank + rot_dim).to(q_out.dtype)
-    v = c.view(n, 1, kv_rank).to(q_out.dtype)
+    dtype = (k_new if k_new is not None else k_pages).dtype
+    k = torch.cat([c, kr], dim=-1).view(n, 1, kv_rank + rot_dim).to(dtype)
+    v = c.view(n, 1, kv_rank).to(dtype)
     if v_new is None and v_pages is None:          # the caller reads its values out of the keys
         v, v_new, v_pages = k, k_new, k_pages
     _store_kv(k, v, positions, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
+
+
+def sigmoid_gate(x, gate, col0, bias=None):
+    z = gate.float().sum(0)[:, col0:col0 + x.shape[1]]
+    if bias is not None:
+        z = z + bias.float()
+    x.copy_((x.float() * torch.sigmoid(z)).to(x.dtype))
+
+
+NORM_MAX_GROUPS = 64
+
+
+def gated_add_group_rmsnorm(residual, branch, gate, gate_bias, post_w, post_groups, post_eps, weight, groups, eps, out,
+                            rows=None):
+    def grouped(v, g, e):
+        p = v.view(v.shape[0], g, -1)
+        return (p * torch.rsqrt((p * p).mean(-1, keepdim=True) + e)).reshape(v.shape)
+
+    idx = slice(None) if rows is None else rows.long()
+    if branch is not None:
+        y = branch.sum(0)[idx]
+        if gate is not None:
+            z = gate.sum(0)[idx]
+            if gate_bias is not None:
+                z = z + gate_bias.float()
+            y = y * torch.sigmoid(z)
+        if post_w is not None:
+            y = grouped(y, post_groups, post_eps) * post_w.float()
+        residual[idx] += y
+    out.copy_((grouped(residual[idx], groups, eps) * weight.float()).to(out.dtype))
+
+
+MINGRU_PIECE = 4
+
+
+def mingru_pieces(max_count):
+    return -(-max_count // MINGRU_PIECE)
+
+
+def mingru_scan(rows, bias, state, slots, cu_tokens, out, carry=None):
+    x = rows.float().sum(0)
+    size = out.shape[1]
+    z = torch.sigmoid(x[:, :size] + bias[:size].float())
+    u = x[:, size:2 * size] + bias[size:].float()
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    g = x[:, 2 * size:]
+    for b in range(slots.numel()):
+        s = state[int(slots[b])].clone()
+        for t in range(int(cu_tokens[b]), int(cu_tokens[b + 1])):
+            s = (1 - z[t]) * s + z[t] * cand[t]
+            out[t] = (s * g[t] * torch.sigmoid(g[t])).to(out.dtype)
+        state[int(slots[b])] = s
+
+
+def tanh_cap(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
 
 
 def head_linear(x, w, y):
@@ -167,13 +236,37 @@ def moe_row_capacity(pairs, n_experts, tile=MOE_TILE_ROWS):
     return -(-cap // tile) * tile
 
 
-def moe_route(x, w_router, b_router, choice, weight):
+class RouterRule:
+    def __init__(self, score="softmax", groups=0, keep_groups=0, group_score_top=2, weight_scale=1.0, weight_sum_eps=0.0):
+        self.score, self.groups, self.keep_groups, self.group_score_top = score, groups, keep_groups, group_score_top
+        self.weight_scale, self.weight_sum_eps = weight_scale, weight_sum_eps
+
+
+def moe_route(x, w_router, b_router, choice, weight, rule=None, extra_out=None):
     z = x.float() @ w_router.float().t()
+    if extra_out is not None:
+        extra_out.copy_(torch.sigmoid(z[:, -1]))
+        z = z[:, :-1]
     if b_router is not None:
         z = z + b_router.float()
-    val, idx = torch.topk(z, choice.shape[1], dim=-1)
+    top = choice.shape[1]
+    if rule is None or rule.score == "softmax":
+        val, idx = torch.topk(z, top, dim=-1)
+        choice.copy_(idx.to(torch.int32))
+        weight.copy_(torch.softmax(val, dim=-1))
+        return
+    s = torch.sigmoid(z)
+    n, n_exp = s.shape
+    masked = s
+    if rule.groups:
+        per = n_exp // rule.groups
+        gs = torch.topk(s.view(n, rule.groups, per), min(rule.group_score_top, per), dim=-1).values.sum(-1)
+        best = torch.topk(gs, rule.keep_groups, dim=-1).indices
+        ok = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, best, True)
+        masked = s.masked_fill(~ok[:, :, None].expand(-1, -1, per).reshape(n, n_exp), -1.0)
+    val, idx = torch.topk(masked, top, dim=-1)
     choice.copy_(idx.to(torch.int32))
-    weight.copy_(torch.softmax(val, dim=-1))
+    weight.copy_(val / (val.sum(-1, keepdim=True) + rule.weight_sum_eps) * rule.weight_scale)
 
 
 def moe_plan(choice, n_experts, row_of_pair, token_of_row, tile_expert):
@@ -219,12 +312,12 @@ def moe_down(act, tile_expert, w_down, y):
             y[r] = w_down[e].float() @ act[r].float()
 
 
-def moe_combine(y, row_of_pair, weight, shared, out):
+def moe_combine(y, row_of_pair, weight, shared, out, shared_scale=None):
     n, top = weight.shape
     rows = row_of_pair.view(n, top).long()
     out.copy_((weight[:, :, None] * y[rows]).sum(1))
     if shared is not None:
-        out += shared.sum(0)
+        out += shared.sum(0) if shared_scale is None else shared.sum(0) * shared_scale[:, None]
 
 
 def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, seq_of_token, slots,
@@ -243,12 +336,19 @@ def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, 
             v_pages[pg, hh, off] = v_new[t, h]
 
 
-def silu_mul(gate_up, out):
+GATE_ACTIVATIONS = ("silu", "gelu_tanh")
+
+
+def silu_mul(gate_up, out, activation="silu"):
     x = gate_up.float().sum(0)
     inter = out.shape[1]
     half = x.shape[1] // 2
     g, u = x[:, :inter], x[:, half:half + inter]
-    out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+    if activation == "gelu_tanh":
+        a = 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    else:
+        a = g / (1 + torch.exp(-g))
+    out.copy_((a * u).to(out.dtype))
 
 
 def hc_max_streams():
