@@ -39,6 +39,8 @@ SOURCES: Dict[str, List[str]] = {
     "block_runner": ["block_runner.cu", "kernel_args.h"],
     "layernorm": ["layernorm.cu", "common.cuh", "kernel_args.h"],
     "latent": ["latent.cu", "common.cuh", "kernel_args.h"],
+    "groupnorm": ["groupnorm.cu", "common.cuh", "kernel_args.h"],
+    "recurrent": ["recurrent.cu", "common.cuh", "kernel_args.h"],
     "moe": ["moe.cu", "common.cuh", "kernel_args.h"],
 }
 

@@ -653,9 +653,10 @@ LLG_API int llg_kv_write(const void* k_new, const void* v_new, void* k_pages, vo
 // to a multiple P of 128, then the up rows in the same way (the layout the tensor-core product's
 // gated epilogue wants).  A product's output row therefore holds, for feature i, g at i and u at P + i:
 // out[n][i] = silu(g) * u, silu(g) = g / (1 + exp(-g))  (Daisi.Llogos.Cpu/Silu.cs:9-16).
+// `act`: what the gate passes: 2 silu, 1 the tanh form of gelu (the kinds of llg_act in common.cuh).
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long long partial_stride,
-                                OT* __restrict__ out, long long total, int inter, int width) {
+                                OT* __restrict__ out, long long total, int inter, int width, int act) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -668,12 +669,27 @@ __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long 
       g += to_f32(p[s * partial_stride]);
       u += to_f32(p[s * partial_stride + width / 2]);
     }
-    out[idx] = from_f32<OT>(g / (1.0f + expf(-g)) * u);
+    out[idx] = from_f32<OT>((act == 2 ? g / (1.0f + expf(-g)) : llg_act(act, g)) * u);
   }
 }
 
+static int gate_mul(const void* gu, int in_dtype, int n_partials, long long partial_stride, void* out,
+                    int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream);
+
 LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long partial_stride, void* out,
                          int out_dtype, int n_tokens, int inter, cudaStream_t stream) {
+  return gate_mul(gu, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, 2, stream);
+}
+
+// out[n][i] = act(g) * u with the gate's activation given by its kind (llg_act in common.cuh).
+LLG_API int llg_gate_mul(const void* gu, int in_dtype, int n_partials, long long partial_stride, void* out,
+                         int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream) {
+  LLG_REQUIRE(act >= 0 && act < LLG_ACT_KINDS, "gate_mul: activation kind %d is not known", act);
+  return gate_mul(gu, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, act, stream);
+}
+
+static int gate_mul(const void* gu, int in_dtype, int n_partials, long long partial_stride, void* out,
+                    int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && inter > 0 && n_partials >= 1, "silu_mul: bad sizes");
   const long long total = (long long)n_tokens * inter;
   if (total == 0) return 0;
@@ -683,7 +699,7 @@ LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long
   if (blocks > (long long)llg_sm_count() * 16) blocks = (long long)llg_sm_count() * 16;
 #define LAUNCH(IT, OT)                                                                                          \
   silu_mul_kernel<IT, OT><<<(unsigned)blocks, threads, 0, stream>>>((const IT*)gu, n_partials, partial_stride, \
-                                                                     (OT*)out, total, inter, width)
+                                                                     (OT*)out, total, inter, width, act)
   if (in_dtype == LLG_F32 && out_dtype == LLG_F32) LAUNCH(float, float);
   else if (in_dtype == LLG_F32 && out_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
   else if (in_dtype == LLG_BF16 && out_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -1170,4 +1186,22 @@ LLG_API int llg_act_rows(const void* in, int in_dtype, int n_partials, long long
   else return llg_fail("act_rows: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
 #undef LAUNCH
   return llg_check_launch("act_rows");
+}
+
+// ---- a cap on logits ----------------------------------------------------------------------
+// x <- cap * tanh(x / cap), in place (float32).
+__global__ void tanh_cap_kernel(float* __restrict__ x, long long total, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+LLG_API int llg_tanh_cap(float* x, long long total, float cap, cudaStream_t stream) {
+  LLG_REQUIRE(total >= 0 && cap > 0.f, "tanh_cap: bad arguments (cap %g)", cap);
+  if (total == 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)llg_sm_count() * 16) blocks = (long long)llg_sm_count() * 16;
+  llg_launch(tanh_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, total, cap);
+  return llg_check_launch("tanh_cap");
 }

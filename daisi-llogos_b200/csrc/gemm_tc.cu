@@ -125,6 +125,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+// What the gate of a gated epilogue passes: act 0 silu, else kind act - 1 of llg_act (common.cuh).  The choice is the
+// same for every element of a launch.
+__device__ __forceinline__ float gate_act(int act, float g) {
+  return act == 0 ? __fdividef(g, 1.0f + __expf(-g)) : llg_act(act - 1, g);
+}
+
 struct GemmParams {
   void* out;        // [splits][n][o], or [n][gated_features] with the gated epilogue
   int n, o, k;
@@ -136,6 +142,7 @@ struct GemmParams {
   RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
   int act;          // EPI -1 (the plain epilogue with an activation; one split): kind + 1, every element goes through
                     // llg_act(kind, .) before it is stored.  A variant of its own, so that the plain products carry none of it.
+                    // EPI 1 (the gated epilogue): 0 = the gate passes silu, else kind + 1 of the gate's activation.
   // Grouped products (SWAP 1, one token tile per block): token tile t multiplies with the matrix of group tile_group[t],
   // whose rows start at row tile_group[t] * group_rows of w; a tile whose group is negative is left out by every role.
   // The list is written by a kernel earlier in the step, so nothing of w is requested ahead of the dependency wait.
@@ -541,7 +548,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                   const float g = __uint_as_float(r[c]) * rs;
-                  v[c] = __fdividef(g, 1.0f + __expf(-g)) * (__uint_as_float(ru[c]) * rs);
+                  v[c] = gate_act(p.act, g) * (__uint_as_float(ru[c]) * rs);
                 }
               } else {
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -640,7 +647,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 for (int c = 0; c < 16; ++c) {
                   const float rs = p.scale.ss ? col_scale[c0 + 16 * q + c] : 1.0f;
                   const float g = __uint_as_float(rg[q][c]) * rs, u = __uint_as_float(ru[q][c]) * rs;
-                  v[c] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                  v[c] = gate_act(p.act, g) * u;
                 }
                 OT* dst = out + (long long)(n0 + c0 + 16 * q) * inter + f;
   #pragma unroll
@@ -770,6 +777,15 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   return gemm_tc_run(x, w, out, out_dtype, n, o, k, splits, tile_n, gated_features, scale, 0, stream);
 }
 
+// The gated product (llg_gemm_tc with gated_features > 0) with another activation of the gate than silu: out[n][F] =
+// act(gate) * up, kind as in llg_act (common.cuh).
+LLG_API int llg_gemm_tc_gated(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int tile_n,
+                              int gated_features, int kind, const RowScale* scale, cudaStream_t stream) {
+  LLG_REQUIRE(kind >= 0 && kind < LLG_ACT_KINDS && gated_features > 0, "gemm_tc_gated: activation kind %d, %d features", kind,
+              gated_features);
+  return gemm_tc_run(x, w, out, out_dtype, n, o, k, 1, tile_n, gated_features, scale, kind == 2 ? 0 : kind + 1, stream);
+}
+
 // out[n][o] = act(x w^T) in one split, the activation (kind as in llg_act, common.cuh) applied to the float32 sums
 // before they are rounded to the output type: the up product of an ungated feed-forward.
 LLG_API int llg_gemm_tc_act(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int kind,
@@ -786,8 +802,8 @@ static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, i
   splits = llg_gemm_tc_splits(k, splits);
   LLG_REQUIRE(out_dtype == LLG_F32 || (out_dtype == LLG_BF16 && splits == 1), "gemm_tc: bfloat16 output needs one split");
   const bool gated = gated_features > 0;
-  LLG_REQUIRE(act == 0 || (splits == 1 && !gated && out_dtype == LLG_BF16),
-              "gemm_tc: an activation needs one split, no gating and bfloat16 output");
+  LLG_REQUIRE(act == 0 || gated || (splits == 1 && out_dtype == LLG_BF16),
+              "gemm_tc: an activation needs one split and bfloat16 output");
   LLG_REQUIRE(!gated || (splits == 1 && o == ((gated_features + BM - 1) / BM) * 2 * BM),
               "gemm_tc: the gated epilogue needs one split and ceil(features / 128) * 256 rows of w (features=%d rows=%d splits=%d)",
               gated_features, o, splits);

@@ -226,13 +226,84 @@ struct LayerNormArgs {
   int n_out, hidden;
 };
 
-// Preparation for latent attention (latent.cu: latent_prep).  A row of the input product holds, per token,
-// nh * (dim + rdim) query elements (head by head: dim unrotated, rdim rotated), then `rank` latent elements, then rdim
-// elements of the key part that all heads share.
-struct LatentPrepArgs {
-  const float* rows;          // [n_partials][n_tokens][nh * (dim + rdim) + rank + rdim]
+// RMS norm in groups fused with the residual add, the add optionally through a gate and a norm of its own
+// (groupnorm.cu).  For output row j (token r = rows ? rows[j] : j), with y = the sum of branch's partials:
+//   y *= sigmoid(sum of gate's partials + gate_bias)          where gate is given
+//   y  = group_rms(y, post_groups, post_eps) * post_w         where post_w is given
+//   v  = residual[r] + y                                      (written back where branch is given)
+//   out[j] = group_rms(v, groups, eps) * weight
+// group_rms(v, g, e): v in g equal consecutive parts, each divided by sqrt(mean(part^2) + e).
+#define LLG_NORM_MAX_GROUPS 64
+struct GroupNormArgs {
+  float* residual;            // [n_tokens][hidden]
+  const float* branch;        // [n_partials][n_tokens][hidden] or null
+  int n_partials;
+  const float* gate;          // [gate_partials][n_tokens][hidden] or null
+  int gate_partials;
+  long long partial_stride;   // elements between partials of either (n_tokens * hidden)
+  const float* gate_bias;     // [hidden] or null
+  const void* post_w;         // [hidden] or null, stored as weight is
+  int post_groups;
+  float post_eps;
+  const void* weight;         // [hidden]
+  int w_dtype;
+  int groups;
+  float eps;
+  void* out;                  // [n_out][hidden]
+  int out_dtype;
+  const int* rows;            // [n_out] or null
+  int n_out, hidden;
+};
+
+// The minGRU recurrence over a step's sequences (recurrent.cu).  Row n of the input product holds z | u | g arguments
+// (3 * size columns); per channel S_t = (1 - z_t) S_{t-1} + z_t c_t with z = sigmoid(. + bias[0..size)), u = . +
+// bias[size..2 size), c = u + 1/2 (u >= 0) or sigmoid(u); out[n] = S_t * silu(g).  state[slot] holds S before the step's
+// first token and receives S after its last.  A step whose longest sequence brings more than LLG_MINGRU_PIECE tokens is
+// scanned in pieces of that many (the recurrence is linear in S): carry [n_seqs][pieces][2][size] receives every
+// piece's (product of 1 - z, state reached from zero); a second kernel walks a sequence's pieces from its state, leaves
+// each piece's starting state in the second field and the last state in state[slot]; the scan then runs again, every
+// piece from its own starting state, and writes the outputs.  Without carry one kernel does it all.
+#define LLG_MINGRU_PIECE 64
+struct MinGruArgs {
+  const float* rows;          // [n_partials][n_tokens][3 * size]
   int n_partials;
   long long partial_stride;
+  const float* bias;          // [2 * size]
+  float* state;               // [slots][size]
+  const int* slots;           // [n_seqs]
+  const int* cu_tokens;       // [n_seqs + 1]
+  void* out;                  // [n_tokens][size]
+  int out_dtype;
+  float* carry;               // or null: no sequence brings more than one piece
+  int pieces;                 // pieces per sequence in carry
+  int n_seqs, n_tokens, size;
+};
+
+// How a router turns logits into a token's experts and their weights (moe.cu).
+//   score 0: the `top` largest logits, weights = softmax over them.
+//   score 1: s = sigmoid(logit); with groups > 0 the experts form that many equal groups of neighbours, a group's
+//            score is the sum of its group_top largest s, and only experts of the keep_groups best groups are eligible;
+//            the `top` eligible experts of largest s, weights = s / (sum of the chosen s + sum_eps) * scale.
+struct RouterRule {
+  int score;
+  int groups, keep_groups, group_top;
+  float scale, sum_eps;
+};
+
+// Preparation for latent attention (latent.cu: latent_prep).  A row of the input product holds, per token, up to three
+// runs of columns, each at a column of its own (negative: the run is absent and its part of the work is left out):
+// at q_col nh * (dim + rdim) query elements (head by head: dim unrotated, rdim rotated); at kv_col `rank` latent
+// elements, then rdim elements of the key part that all heads share; at cq_col cq_rank elements of a latent of the
+// queries, which is RMS-normed with cq_norm_w and written to cq_out for the product that makes the queries from it.
+// Other columns of the row (row_width in all) are someone else's.
+struct LatentPrepArgs {
+  const float* rows;          // [n_partials][n_tokens][row_width]
+  int n_partials;
+  long long partial_stride;
+  int row_width, q_col, kv_col, cq_col, cq_rank;
+  const void* cq_norm_w;      // [cq_rank], stored as c_norm_w is
+  void* cq_out;               // [n_tokens][cq_rank], in the output type
+  int pairing;                // which elements a rotation pairs: 0 (i, i + rdim/2), 1 (2i, 2i+1)
   const void* c_norm_w;       // [rank]
   int w_dtype;
   float norm_eps;

@@ -8,6 +8,7 @@
 //                 pages), the queries' rotated parts behind
 //                 the place where head_linear puts the unrotated parts' products, and the unrotated parts by themselves.
 //   head_linear : y[n][h][:] = W_h x[n][h][:], a small product per (token, head) with one matrix per head; float32 sums.
+//   sigmoid_gate: x *= sigmoid(columns of a product's float32 partial sums), in place (the gate on the concatenated heads).
 //
 // Statistics, angles' tables and sums are float32; inputs and outputs float32 or bfloat16.
 #include "common.cuh"
@@ -17,42 +18,60 @@ LLG_API const char* llg_last_error() { return g_llg_error; }
 
 namespace {
 
-// one warp per unit: unit 0 .. nh-1 = a query head, unit nh = latent and shared key part
+// One warp per unit of a token.  The units a launch has, in this order: the nh query heads (q_col >= 0), the latent with
+// the shared key part (kv_col >= 0), the queries' latent (cq_col >= 0).
 template <typename OT, typename WT>
 __global__ void latent_prep_kernel(LatentPrepArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int units = a.nh + 1;
+  const int q_units = a.q_col >= 0 ? a.nh : 0, kv_units = a.kv_col >= 0 ? 1 : 0;
+  const int units = q_units + kv_units + (a.cq_col >= 0 ? 1 : 0);
   const long long item = (long long)blockIdx.x * warps + warp;
   if (item >= (long long)a.n_tokens * units) return;
   const int n = (int)(item / units), u = (int)(item % units);
   const int qd = a.dim + a.rdim, kd = a.rank + a.rdim, half = a.rdim >> 1;
-  const long long row_w = (long long)a.nh * qd + kd;
-  const float* src = a.rows + (long long)n * row_w;
+  const float* src = a.rows + (long long)n * a.row_width;
   const int pos = a.positions[n];
   const int p = pos < a.table_positions ? pos : a.table_positions - 1;        // bounded; the host checks the tables' reach
   const float* cs = a.cos_table ? a.cos_table + (long long)p * half : nullptr;
   const float* sn = a.sin_table ? a.sin_table + (long long)p * half : nullptr;
+  // the two elements of pair i, counted from the rotated run's first element
+  const int e1_step = a.pairing ? 2 : 1, e1_off = a.pairing ? 1 : half;
   auto summed = [&](long long col) {
     float v = 0.f;
     for (int s = 0; s < a.n_partials; ++s) v += src[s * a.partial_stride + col];
     return v;
   };
-  if (u < a.nh) {
-    const long long col = (long long)u * qd;
+  if (u < q_units) {
+    const long long col = a.q_col + (long long)u * qd;
     OT* qp = (OT*)a.q_plain + ((long long)n * a.nh + u) * a.dim;
     for (int d = lane; d < a.dim; d += 32) qp[d] = from_f32<OT>(summed(col + d));
     OT* qo = (OT*)a.q_out + ((long long)n * a.nh + u) * kd + a.rank;
     for (int i = lane; i < half; i += 32) {
-      const float x0 = summed(col + a.dim + i), x1 = summed(col + a.dim + half + i);
-      qo[i] = from_f32<OT>(x0 * cs[i] - x1 * sn[i]);
-      qo[half + i] = from_f32<OT>(x1 * cs[i] + x0 * sn[i]);
+      const int e0 = i * e1_step, e1 = e0 + e1_off;
+      const float x0 = summed(col + a.dim + e0), x1 = summed(col + a.dim + e1);
+      qo[e0] = from_f32<OT>(x0 * cs[i] - x1 * sn[i]);
+      qo[e1] = from_f32<OT>(x1 * cs[i] + x0 * sn[i]);
     }
     return;
   }
+  const WT* w = (const WT*)(u < q_units + kv_units ? a.c_norm_w : a.cq_norm_w);
+  if (u >= q_units + kv_units) {
+    // the queries' latent: RMS norm over its cq_rank elements
+    float ss = 0.f;
+    for (int d = lane; d < a.cq_rank; d += 32) {
+      const float v = summed(a.cq_col + d);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)a.cq_rank + a.norm_eps);
+    OT* o = (OT*)a.cq_out + (long long)n * a.cq_rank;
+    for (int d = lane; d < a.cq_rank; d += 32) o[d] = from_f32<OT>(summed(a.cq_col + d) * inv * to_f32(w[d]));
+    return;
+  }
   // the latent: RMS norm over its kv_rank elements
-  const long long col = (long long)a.nh * qd;
+  const long long col = a.kv_col;
   float ss = 0.f;
   for (int d = lane; d < a.rank; d += 32) {
     const float v = summed(col + d);
@@ -69,7 +88,6 @@ __global__ void latent_prep_kernel(LatentPrepArgs a) {
     kp = (OT*)a.k_pages + r * kd;
     vp = a.v_pages ? (OT*)a.v_pages + r * a.rank : nullptr;
   }
-  const WT* w = (const WT*)a.c_norm_w;
   for (int d = lane; d < a.rank; d += 32) {
     const OT c = from_f32<OT>(summed(col + d) * inv * to_f32(w[d]));
     if (kn) kn[d] = c;
@@ -78,11 +96,29 @@ __global__ void latent_prep_kernel(LatentPrepArgs a) {
     if (vp) vp[d] = c;
   }
   for (int i = lane; i < half; i += 32) {
-    const float x0 = summed(col + a.rank + i), x1 = summed(col + a.rank + half + i);
+    const int e0 = i * e1_step, e1 = e0 + e1_off;
+    const float x0 = summed(col + a.rank + e0), x1 = summed(col + a.rank + e1);
     const OT r0 = from_f32<OT>(x0 * cs[i] - x1 * sn[i]), r1 = from_f32<OT>(x1 * cs[i] + x0 * sn[i]);
-    if (kn) { kn[a.rank + i] = r0; kn[a.rank + half + i] = r1; }
-    if (kp) { kp[a.rank + i] = r0; kp[a.rank + half + i] = r1; }
+    if (kn) { kn[a.rank + e0] = r0; kn[a.rank + e1] = r1; }
+    if (kp) { kp[a.rank + e0] = r0; kp[a.rank + e1] = r1; }
   }
+}
+
+// x[n][j] *= sigmoid(sum of the partials gate[.][n][col0 + j] + bias[j]): a gate whose arguments are columns of another
+// product's float32 partial sums, applied in place.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__ gate, int n_partials, long long partial_stride,
+                                    int gate_width, int col0, const float* __restrict__ bias, long long total, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long n = i / width;
+  const int j = (int)(i % width);
+  const float* g = gate + n * gate_width + col0 + j;
+  float z = bias ? bias[j] : 0.f;
+  for (int s = 0; s < n_partials; ++s) z += g[s * partial_stride];
+  x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-z)));
 }
 
 // y[n][h][o] = sum_k w[h][o][k] x[n][h][k].  A block takes TN tokens of one head and TO outputs; x's tile lies in shared
@@ -141,13 +177,21 @@ LLG_API int llg_latent_prep(const LatentPrepArgs* args, int out_dtype, cudaStrea
   const LatentPrepArgs& a = *args;
   LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.dim > 0 && a.rank > 0 && a.rdim >= 0 && a.rdim % 2 == 0, "latent_prep: bad sizes");
   LLG_REQUIRE(a.n_partials >= 1, "latent_prep: n_partials must be >= 1");
+  LLG_REQUIRE(a.pairing == 0 || a.pairing == 1, "latent_prep: pairing %d is not known", a.pairing);
+  LLG_REQUIRE(a.q_col < 0 || (a.q_plain && a.q_out && a.q_col + (long long)a.nh * (a.dim + a.rdim) <= a.row_width),
+              "latent_prep: the queries' columns need their outputs and must lie inside the row");
+  LLG_REQUIRE(a.kv_col < 0 || a.kv_col + a.rank + a.rdim <= a.row_width, "latent_prep: the latent's columns must lie inside the row");
+  LLG_REQUIRE(a.cq_col < 0 || (a.cq_rank > 0 && a.cq_norm_w && a.cq_out && a.cq_col + a.cq_rank <= a.row_width),
+              "latent_prep: the queries' latent needs its size, weight and output and must lie inside the row");
+  LLG_REQUIRE(a.kv_col >= 0 || (!a.k_new && !a.k_pages), "latent_prep: keys are written where the latent is given");
   LLG_REQUIRE(a.rdim == 0 || (a.cos_table && a.sin_table && a.table_positions > 0), "latent_prep: rotated elements need the tables");
   LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
               "latent_prep: a cache write needs page_table, slots and seq_of_token");
   LLG_REQUIRE((!a.v_new || a.k_new) && (!a.v_pages || a.k_pages), "latent_prep: values are written beside keys only");
   if (a.n_tokens == 0) return 0;
   const int warps = 4;
-  const long long items = (long long)a.n_tokens * (a.nh + 1);
+  const long long items = (long long)a.n_tokens * ((a.q_col >= 0 ? a.nh : 0) + (a.kv_col >= 0 ? 1 : 0) + (a.cq_col >= 0 ? 1 : 0));
+  if (items == 0) return 0;
   const unsigned grid = (unsigned)((items + warps - 1) / warps);
   const bool wb = a.w_dtype == LLG_BF16;
   if (out_dtype == LLG_F32) {
@@ -173,4 +217,21 @@ LLG_API int llg_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_t 
     llg_launch(head_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, a);
   else return llg_fail("head_linear: unknown dtype %d", dtype);
   return llg_check_launch("head_linear");
+}
+
+LLG_API int llg_sigmoid_gate(void* x, int dtype, const float* gate, int n_partials, long long partial_stride, int gate_width,
+                             int col0, const float* bias, int n_tokens, int width, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && width > 0 && n_partials >= 1 && col0 >= 0 && col0 + width <= gate_width,
+              "sigmoid_gate: bad sizes (width %d at column %d of %d)", width, col0, gate_width);
+  if (n_tokens == 0) return 0;
+  const long long total = (long long)n_tokens * width;
+  const unsigned grid = (unsigned)((total + 255) / 256);
+  if (dtype == LLG_F32)
+    llg_launch(sigmoid_gate_kernel<float>, dim3(grid), dim3(256), 0, stream, (float*)x, gate, n_partials, partial_stride,
+               gate_width, col0, bias, total, width);
+  else if (dtype == LLG_BF16)
+    llg_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)x, gate, n_partials,
+               partial_stride, gate_width, col0, bias, total, width);
+  else return llg_fail("sigmoid_gate: unknown dtype %d", dtype);
+  return llg_check_launch("sigmoid_gate");
 }

@@ -2,7 +2,8 @@
 // on the CUDA cores, and the weighted sum (argument blocks and the layout in kernel_args.h).
 //
 //   moe_route   : z = W_r x + b in float32 (x may be bfloat16), the `top` largest per token (ties: the lower index), weights
-//                 softmax over the chosen z alone.
+//                 softmax over the chosen z alone; or, by a RouterRule, sigmoid scores chosen within the best groups of
+//                 experts and divided by their sum.
 //   moe_plan    : one block counts the pairs of every expert, lays the experts' runs out one after another, each filled
 //                 up to whole tiles, and gives every pair its row.  Which row of its expert's run a pair gets depends on
 //                 the order in which the threads arrive; no result depends on it (a row's values come from its own token
@@ -20,28 +21,59 @@ LLG_API int llg_moe_max_top() { return LLG_MOE_MAX_TOP; }
 
 namespace {
 
-template <typename XT>
-__global__ void __launch_bounds__(128) moe_route_kernel(const XT* __restrict__ x, const float* __restrict__ w,
-                                                        const float* __restrict__ bias, int* __restrict__ choice,
-                                                        float* __restrict__ weight, int hidden, int n_exp, int top) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ float sm[];
-  float* xs = sm;                   // [hidden]
-  float* z = sm + hidden;           // [n_exp]
-  __shared__ float chosen[LLG_MOE_MAX_TOP];
-  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_f32(x[(long long)n * hidden + i]);
-  __syncthreads();
-  for (int e = warp; e < n_exp; e += 4) {
-    const float* we = w + (long long)e * hidden;
-    float s = 0.f;
-    for (int i = lane; i < hidden; i += 32) s = fmaf(we[i], xs[i], s);
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+// One warp turns a token's logits z[0 .. n_exp) (shared memory, overwritten) into its `top` experts and their weights by
+// `rule` (RouterRule in kernel_args.h).  Ties go to the lower index.  gsc: n_exp floats of scratch beside z (group
+// scores and the marks of the groups that stay).
+__device__ __forceinline__ void choose_and_weigh(float* z, float* gsc, float* chosen, int n_exp, int top, const RouterRule& rule,
+                                                 int* __restrict__ choice, float* __restrict__ weight, int lane) {
+  if (rule.score == 1) {
+    for (int e = lane; e < n_exp; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    __syncwarp();
+    if (rule.groups > 0) {
+      const int per = n_exp / rule.groups;
+      // a group's score: the sum of its group_top largest scores (a lane per group, the largest taken one after another)
+      for (int g = lane; g < rule.groups; g += 32) {
+        const float* zg = z + g * per;
+        float total = 0.f, prev = INFINITY;
+        int prev_i = -1;
+        for (int t = 0; t < rule.group_top && t < per; ++t) {
+          float best = -INFINITY;
+          int arg = -1;
+          for (int i = 0; i < per; ++i) {
+            const float v = zg[i];
+            const bool after = v < prev || (v == prev && i > prev_i);     // not taken yet
+            if (after && v > best) { best = v; arg = i; }
+          }
+          if (arg < 0) break;
+          total += best;
+          prev = best;
+          prev_i = arg;
+        }
+        gsc[g] = total;
+      }
+      __syncwarp();
+      // the keep_groups best groups stay: their mark is 2 (no sum of scores reaches it), the others' scores fall to -1
+      for (int k = 0; k < rule.keep_groups; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int g = lane; g < rule.groups; g += 32) {
+          const float v = gsc[g];
+          if (v <= (float)per && v > best) { best = v; arg = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+          if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0 && arg != 0x7fffffff) gsc[arg] = 2.0f * (float)per + 1.0f;
+        __syncwarp();
+      }
+      for (int e = lane; e < n_exp; e += 32)
+        if (gsc[e / per] <= (float)per) z[e] = -1.0f;
+      __syncwarp();
+    }
   }
-  __syncthreads();
-  if (warp != 0) return;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -57,25 +89,63 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const XT* __restrict__ x
     }
     if (arg == 0x7fffffff) arg = 0;                 // nothing but -inf or NaN left: still a valid index
     if (lane == 0) {
-      choice[(long long)n * top + k] = arg;
+      choice[k] = arg;
       chosen[k] = best;
       z[arg] = -INFINITY;
     }
     __syncwarp();
   }
+  if (rule.score == 1) {
+    // the chosen scores divided by their sum
+    const float sv = lane < top ? chosen[lane] : 0.f;
+    const float total = warp_sum(sv);
+    if (lane < top) weight[lane] = sv / (total + rule.sum_eps) * rule.scale;
+    return;
+  }
   // softmax over the chosen logits; the first chosen is the largest
   const float m = chosen[0];
   float ev = lane < top ? expf(chosen[lane] - m) : 0.f;
   const float total = warp_sum(ev);
-  if (lane < top) weight[(long long)n * top + lane] = ev / total;
+  if (lane < top) weight[lane] = ev / total;
 }
 
-// The same choice from logits that a product has left as float32 partial sums [n_partials][n_tokens][n_exp] (the router's
-// matrix product on the tensor cores, where the checkpoint stores the router in the compute type): a warp per token adds
-// the partials and the bias, then chooses and weighs as moe_route does.
+// A token's logits z = W_r x + b with float32 sums, then choose_and_weigh.  With `extra` the matrix has one more row
+// behind the experts': extra[n] = sigmoid(that row . x).
+template <typename XT>
+__global__ void __launch_bounds__(128) moe_route_kernel(const XT* __restrict__ x, const float* __restrict__ w,
+                                                        const float* __restrict__ bias, int* __restrict__ choice,
+                                                        float* __restrict__ weight, int hidden, int n_exp, int top,
+                                                        RouterRule rule, float* __restrict__ extra) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* xs = sm;                   // [hidden]
+  float* z = sm + hidden;           // [n_exp + 1], then [n_exp] of scratch
+  __shared__ float chosen[LLG_MOE_MAX_TOP];
+  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_f32(x[(long long)n * hidden + i]);
+  __syncthreads();
+  const int rows = n_exp + (extra ? 1 : 0);
+  for (int e = warp; e < rows; e += 4) {
+    const float* we = w + (long long)e * hidden;
+    float s = 0.f;
+    for (int i = lane; i < hidden; i += 32) s = fmaf(we[i], xs[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (bias && e < n_exp ? bias[e] : 0.f);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  if (extra && lane == 0) extra[n] = 1.0f / (1.0f + expf(-z[n_exp]));
+  choose_and_weigh(z, z + n_exp + 1, chosen, n_exp, top, rule, choice + (long long)n * top, weight + (long long)n * top, lane);
+}
+
+// The same choice from logits that a product has left as float32 partial sums [n_partials][n_tokens][width] (the router's
+// matrix product on the tensor cores, where the checkpoint stores the router in the compute type; width = n_exp, or with
+// `extra` n_exp + 1): a warp per token adds the partials and the bias, then chooses and weighs as moe_route does.
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int n_partials, long long partial_stride,
                                                        const float* __restrict__ bias, int* __restrict__ choice,
-                                                       float* __restrict__ weight, int n_tokens, int n_exp, int top) {
+                                                       float* __restrict__ weight, int n_tokens, int n_exp, int top,
+                                                       RouterRule rule, float* __restrict__ extra) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -83,39 +153,17 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 4 + warp;
   if (n >= n_tokens) return;
-  float* z = sm + warp * n_exp;
-  float* chosen = chosen_all[warp];
-  for (int e = lane; e < n_exp; e += 32) {
-    float v = bias ? bias[e] : 0.f;
-    for (int s = 0; s < n_partials; ++s) v += logits[s * partial_stride + (long long)n * n_exp + e];
+  const int width = n_exp + (extra ? 1 : 0);
+  float* z = sm + warp * (2 * n_exp + 1);
+  for (int e = lane; e < width; e += 32) {
+    float v = bias && e < n_exp ? bias[e] : 0.f;
+    for (int s = 0; s < n_partials; ++s) v += logits[s * partial_stride + (long long)n * width + e];
     z[e] = v;
   }
   __syncwarp();
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int arg = 0x7fffffff;
-    for (int e = lane; e < n_exp; e += 32) {
-      const float v = z[e];
-      if (v > best) { best = v; arg = e; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-    }
-    if (arg == 0x7fffffff) arg = 0;
-    if (lane == 0) {
-      choice[(long long)n * top + k] = arg;
-      chosen[k] = best;
-      z[arg] = -INFINITY;
-    }
-    __syncwarp();
-  }
-  const float m = chosen[0];
-  float ev = lane < top ? expf(chosen[lane] - m) : 0.f;
-  const float total = warp_sum(ev);
-  if (lane < top) weight[(long long)n * top + lane] = ev / total;
+  if (extra && lane == 0) extra[n] = 1.0f / (1.0f + expf(-z[n_exp]));
+  choose_and_weigh(z, z + n_exp + 1, chosen_all[warp], n_exp, top, rule, choice + (long long)n * top, weight + (long long)n * top,
+                   lane);
 }
 
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int top, int n_exp,
@@ -366,7 +414,8 @@ __global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int* _
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
-                                   long long shared_stride, float* __restrict__ out, int hidden, int top) {
+                                   long long shared_stride, const float* __restrict__ shared_scale, float* __restrict__ out,
+                                   int hidden, int top) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -376,8 +425,9 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
       const int row = row_of_pair[(long long)n * top + k];
       v = fmaf(weight[(long long)n * top + k], y[(long long)row * hidden + d], v);
     }
-    for (int s = 0; s < n_shared; ++s) v += shared[s * shared_stride + (long long)n * hidden + d];
-    out[(long long)n * hidden + d] = v;
+    float sh = 0.f;
+    for (int s = 0; s < n_shared; ++s) sh += shared[s * shared_stride + (long long)n * hidden + d];
+    out[(long long)n * hidden + d] = v + (shared_scale ? shared_scale[n] * sh : sh);
   }
 }
 
@@ -385,7 +435,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 // the others, so the few rows of a decode step are not a chain of waits.
 __global__ void moe_combine_vec4_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                         const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
-                                        long long shared_stride, float* __restrict__ out, int hidden, int top) {
+                                        long long shared_stride, const float* __restrict__ shared_scale,
+                                        float* __restrict__ out, int hidden, int top) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -398,48 +449,69 @@ __global__ void moe_combine_vec4_kernel(const float* __restrict__ y, const int* 
     const float4 u = *reinterpret_cast<const float4*>(y + (long long)row * hidden + d);
     v.x = fmaf(wk, u.x, v.x); v.y = fmaf(wk, u.y, v.y); v.z = fmaf(wk, u.z, v.z); v.w = fmaf(wk, u.w, v.w);
   }
+  float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < n_shared; ++s) {
     const float4 u = *reinterpret_cast<const float4*>(shared + s * shared_stride + (long long)n * hidden + d);
-    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    sh.x += u.x; sh.y += u.y; sh.z += u.z; sh.w += u.w;
   }
+  const float sc = shared_scale ? shared_scale[n] : 1.0f;
+  v.x = fmaf(sc, sh.x, v.x); v.y = fmaf(sc, sh.y, v.y); v.z = fmaf(sc, sh.z, v.z); v.w = fmaf(sc, sh.w, v.w);
   *reinterpret_cast<float4*>(out + (long long)n * hidden + d) = v;
 }
 
 }  // namespace
 
+static int check_rule(const char* what, const RouterRule& r, int n_exp, int top) {
+  LLG_REQUIRE(r.score == 0 || r.score == 1, "%s: score kind %d is not known", what, r.score);
+  LLG_REQUIRE(r.groups >= 0 && (r.groups == 0 || r.score == 1), "%s: groups of experts go with sigmoid scores", what);
+  if (r.groups > 0) {
+    LLG_REQUIRE(n_exp % r.groups == 0 && r.keep_groups > 0 && r.keep_groups <= r.groups && r.group_top > 0,
+                "%s: %d experts in %d groups of which %d stay, judged by %d scores", what, n_exp, r.groups, r.keep_groups, r.group_top);
+    LLG_REQUIRE(top <= r.keep_groups * (n_exp / r.groups), "%s: top %d exceeds the experts of %d groups", what, top, r.keep_groups);
+  }
+  return 0;
+}
+
+// rule: null = the `top` largest logits weighted by a softmax over them.  extra: null, or [n_tokens] for the sigmoid of one
+// more row of w behind the experts' rows.
 LLG_API int llg_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int* choice, float* weight,
-                          int n_tokens, int hidden, int n_exp, int top, cudaStream_t stream) {
+                          int n_tokens, int hidden, int n_exp, int top, const RouterRule* rule, float* extra, cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && hidden > 0, "moe_route: bad sizes");
   LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_route: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
   LLG_REQUIRE(top > 0 && top <= n_exp && top <= LLG_MOE_MAX_TOP, "moe_route: top %d of %d experts (at most %d)", top, n_exp,
               LLG_MOE_MAX_TOP);
+  const RouterRule r = rule ? *rule : RouterRule{0, 0, 0, 0, 1.0f, 0.0f};
+  if (check_rule("moe_route", r, n_exp, top)) return 1;
   if (n_tokens == 0) return 0;
-  const size_t smem = (size_t)(hidden + n_exp) * sizeof(float);
+  const size_t smem = (size_t)(hidden + 2 * n_exp + 1) * sizeof(float);
   LLG_REQUIRE(smem <= 200 * 1024, "moe_route: rows of %d elements do not fit shared memory", hidden);
   if (x_dtype == LLG_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     llg_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)x, w, bias, choice, weight, hidden,
-               n_exp, top);
+               n_exp, top, r, extra);
   } else if (x_dtype == LLG_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     llg_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)x, w, bias, choice,
-               weight, hidden, n_exp, top);
+               weight, hidden, n_exp, top, r, extra);
   } else {
     return llg_fail("moe_route: unknown dtype %d", x_dtype);
   }
   return llg_check_launch("moe_route");
 }
 
+// logits: [n_partials][n_tokens][n_exp], or with `extra` one more column behind the experts'.
 LLG_API int llg_moe_topk(const float* logits, int n_partials, long long partial_stride, const float* bias, int* choice,
-                         float* weight, int n_tokens, int n_exp, int top, cudaStream_t stream) {
+                         float* weight, int n_tokens, int n_exp, int top, const RouterRule* rule, float* extra, cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && n_partials >= 1, "moe_topk: bad sizes");
   LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_topk: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
   LLG_REQUIRE(top > 0 && top <= n_exp && top <= LLG_MOE_MAX_TOP, "moe_topk: top %d of %d experts (at most %d)", top, n_exp,
               LLG_MOE_MAX_TOP);
+  const RouterRule r = rule ? *rule : RouterRule{0, 0, 0, 0, 1.0f, 0.0f};
+  if (check_rule("moe_topk", r, n_exp, top)) return 1;
   if (n_tokens == 0) return 0;
-  llg_launch(moe_topk_kernel, dim3((n_tokens + 3) / 4), dim3(128), (size_t)4 * n_exp * sizeof(float), stream, logits, n_partials,
-             partial_stride, bias, choice, weight, n_tokens, n_exp, top);
+  llg_launch(moe_topk_kernel, dim3((n_tokens + 3) / 4), dim3(128), (size_t)4 * (2 * n_exp + 1) * sizeof(float), stream, logits,
+             n_partials, partial_stride, bias, choice, weight, n_tokens, n_exp, top, r, extra);
   return llg_check_launch("moe_topk");
 }
 
@@ -546,8 +618,10 @@ LLG_API int llg_moe_gather_rows(const void* x, const int* token_of_row, void* ou
   return llg_check_launch("moe_gather_rows");
 }
 
+// shared_scale: null, or [n_tokens]: the sum of the shared expert's partials is multiplied by it.
 LLG_API int llg_moe_combine(const float* y, const int* row_of_pair, const float* weight, const float* shared, int n_shared,
-                            long long shared_stride, float* out, int n_tokens, int hidden, int top, cudaStream_t stream) {
+                            long long shared_stride, const float* shared_scale, float* out, int n_tokens, int hidden, int top,
+                            cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && top > 0, "moe_combine: bad sizes");
   LLG_REQUIRE(!shared || n_shared >= 1, "moe_combine: a shared expert's partials need at least one");
   if (n_tokens == 0) return 0;
@@ -557,11 +631,11 @@ LLG_API int llg_moe_combine(const float* y, const int* row_of_pair, const float*
     const int threads = 128;
     dim3 grid(n_tokens, (hidden / 4 + threads - 1) / threads);
     llg_launch(moe_combine_vec4_kernel, grid, dim3(threads), 0, stream, y, row_of_pair, weight, shared, shared ? n_shared : 0,
-               shared_stride, out, hidden, top);
+               shared_stride, shared ? shared_scale : nullptr, out, hidden, top);
   } else {
     const int threads = hidden >= 1024 ? 256 : 128;
     llg_launch(moe_combine_kernel, dim3(n_tokens, 1), dim3(threads), 0, stream, y, row_of_pair, weight, shared,
-               shared ? n_shared : 0, shared_stride, out, hidden, top);
+               shared ? n_shared : 0, shared_stride, shared ? shared_scale : nullptr, out, hidden, top);
   }
   return llg_check_launch("moe_combine");
 }

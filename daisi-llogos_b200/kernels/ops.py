@@ -195,9 +195,33 @@ class _LayerNormArgs(Structure):
     ]
 
 
+class _GroupNormArgs(Structure):
+    _fields_ = [
+        ("residual", c_void_p), ("branch", c_void_p), ("n_partials", c_int), ("gate", c_void_p), ("gate_partials", c_int),
+        ("partial_stride", c_longlong), ("gate_bias", c_void_p), ("post_w", c_void_p), ("post_groups", c_int),
+        ("post_eps", c_float), ("weight", c_void_p), ("w_dtype", c_int), ("groups", c_int), ("eps", c_float),
+        ("out", c_void_p), ("out_dtype", c_int), ("rows", c_void_p), ("n_out", c_int), ("hidden", c_int),
+    ]
+
+
+class _MinGruArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong), ("bias", c_void_p), ("state", c_void_p),
+        ("slots", c_void_p), ("cu_tokens", c_void_p), ("out", c_void_p), ("out_dtype", c_int), ("carry", c_void_p),
+        ("pieces", c_int), ("n_seqs", c_int), ("n_tokens", c_int), ("size", c_int),
+    ]
+
+
+class _RouterRule(Structure):
+    _fields_ = [("score", c_int), ("groups", c_int), ("keep_groups", c_int), ("group_top", c_int), ("scale", c_float),
+                ("sum_eps", c_float)]
+
+
 class _LatentPrepArgs(Structure):
     _fields_ = [
         ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("row_width", c_int), ("q_col", c_int), ("kv_col", c_int), ("cq_col", c_int), ("cq_rank", c_int),
+        ("cq_norm_w", c_void_p), ("cq_out", c_void_p), ("pairing", c_int),
         ("c_norm_w", c_void_p), ("w_dtype", c_int), ("norm_eps", c_float),
         ("cos_table", c_void_p), ("sin_table", c_void_p), ("table_positions", c_int), ("positions", c_void_p),
         ("q_plain", c_void_p), ("q_out", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p),
@@ -271,6 +295,8 @@ def _load_lib(name: str):
         lib.llg_kv_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.llg_silu_mul.argtypes = [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.llg_gate_mul.argtypes = [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_tanh_cap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         lib.llg_scatter_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
@@ -285,6 +311,8 @@ def _load_lib(name: str):
         lib.llg_gemm_tc_splits.argtypes = [c_int, c_int]
         lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                     POINTER(_RowScale), c_void_p]
+        lib.llg_gemm_tc_gated.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          POINTER(_RowScale), c_void_p]
         lib.llg_gemm_tc_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, POINTER(_QkPrepArgs), c_void_p]
         lib.llg_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                             c_int, c_void_p]
@@ -311,20 +339,34 @@ def _load_lib(name: str):
         lib.llg_attn_decode_tma_status.restype = c_int
     elif name == "layernorm":
         lib.llg_add_layernorm.argtypes = [POINTER(_LayerNormArgs), c_void_p]
+    elif name == "groupnorm":
+        lib.llg_gated_add_group_rmsnorm.argtypes = [POINTER(_GroupNormArgs), c_void_p]
+        lib.llg_norm_max_groups.restype = c_int
+        if lib.llg_norm_max_groups() != NORM_MAX_GROUPS:
+            raise KernelError(f"the norm kernel takes {lib.llg_norm_max_groups()} groups, Python expects {NORM_MAX_GROUPS}")
+    elif name == "recurrent":
+        lib.llg_mingru_scan.argtypes = [POINTER(_MinGruArgs), c_int, c_void_p]
+        lib.llg_mingru_piece.restype = c_int
+        if lib.llg_mingru_piece() != MINGRU_PIECE:
+            raise KernelError(f"the scan's pieces hold {lib.llg_mingru_piece()} tokens, Python expects {MINGRU_PIECE}")
     elif name == "latent":
         lib.llg_latent_prep.argtypes = [POINTER(_LatentPrepArgs), c_int, c_void_p]
+        lib.llg_sigmoid_gate.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int,
+                                         c_void_p]
         lib.llg_head_linear.argtypes = [POINTER(_HeadLinearArgs), c_int, c_void_p]
     elif name == "moe":
-        lib.llg_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                      POINTER(_RouterRule), c_void_p, c_void_p]
         lib.llg_head_linear_mma_supported.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_int]
         lib.llg_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
                                             c_int, c_int, c_int, c_int, c_void_p]
-        lib.llg_moe_topk.argtypes = [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.llg_moe_topk.argtypes = [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                     POINTER(_RouterRule), c_void_p, c_void_p]
         lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.llg_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.llg_grouped_linear.argtypes = [POINTER(_GroupedLinearArgs), c_int, c_int, c_void_p]
-        lib.llg_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int,
-                                        c_int, c_void_p]
+        lib.llg_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_void_p]
     elif name == "init":
         lib.llg_fill_normal.argtypes = [c_void_p, c_int, c_longlong, c_ulonglong, ctypes.c_double, ctypes.c_double, c_void_p]
         lib.llg_fill.argtypes = [c_void_p, c_int, c_longlong, c_float, c_void_p]
@@ -454,13 +496,16 @@ def gated_rows(features: int) -> int:
     return -(-features // 128) * 256
 
 
+GATE_ACTIVATIONS = ("silu", "gelu_tanh")     # what the gate of a gated feed-forward may pass
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0, gated_features: int = 0,
-            row_scale: Optional[RowScale] = None) -> None:
+            row_scale: Optional[RowScale] = None, gate_activation: str = "silu") -> None:
     """out[s, n, o] = split-K partials of x[n, k] w[o, k] on the tensor cores (tcgen05, TMA).
 
     ``out`` is ``[S, N, O]`` float32 with S = ``gemm_tc_splits(k, wish)``, or ``[1, N, O]`` bfloat16.
     With ``gated_features = F`` the matrix ``w`` is in the gated layout (``gated_rows(F)`` rows) and
-    ``out`` is ``[1, N, F]`` holding ``silu(gate) * up``.  ``row_scale``: what a norm left for the rows of ``x``;
+    ``out`` is ``[1, N, F]`` holding ``act(gate) * up`` with ``act`` = ``gate_activation`` (one of ``GATE_ACTIVATIONS``).  ``row_scale``: what a norm left for the rows of ``x``;
     the rows of the product are multiplied by it (before the gating).
     """
     lib = _lib("gemm_tc")
@@ -470,6 +515,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int 
     assert k == k2 and out.shape == (s, n, gated_features if gated_features else o), (x.shape, w.shape, out.shape)
     if gemm_tc_splits(k, s) != s:
         raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
+    if gate_activation != "silu":
+        if gate_activation not in GATE_ACTIVATIONS or not gated_features:
+            raise KernelError(f"gemm_tc: gate activation '{gate_activation}' (known: {', '.join(GATE_ACTIVATIONS)}; gated products only)")
+        _check(lib, lib.llg_gemm_tc_gated(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, tile_n,
+                                          gated_features, ACTIVATIONS[gate_activation], _scale_ref(row_scale, n), _stream()))
+        return
     _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
                                 tile_n, gated_features, _scale_ref(row_scale, n), _stream()))
 
@@ -699,33 +750,52 @@ def add_layernorm(residual: torch.Tensor, parts, scale: float, weight: torch.Ten
 
 def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int, kv_rank: int, c_norm_w: torch.Tensor,
                 norm_eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
-                q_plain_out: torch.Tensor, q_out: torch.Tensor,
+                q_plain_out: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None,
                 k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
                 k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                 page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
-                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
-    """Preparation for latent attention from the rows of one product, float32 partials ``[P, N, nh (dim + rdim) + rank +
-    rdim]``: the latent (``rank`` elements, RMS-normed with ``c_norm_w``) and the rotated shared key part become the
-    token's key ``[rank + rdim]`` and, where ``v_new`` / ``v_pages`` are given, value ``[rank]`` of ONE key/value head
-    (packed and/or into the cache pages); every
-    query head's unrotated part goes to ``q_plain_out`` ``[N, nh, dim]`` and its rotated part, rotated, to the last
-    ``rdim`` elements of ``q_out`` ``[N, nh, rank + rdim]`` (the first ``rank`` are ``head_linear``'s to fill)."""
+                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                pairing: int = 0, q_col: int = 0, kv_col: Optional[int] = None, cq_col: int = -1,
+                cq_norm_w: Optional[torch.Tensor] = None, cq_out: Optional[torch.Tensor] = None) -> None:
+    """Preparation for latent attention from the rows of one product, float32 partials ``[P, N, width]``.  A row holds up to
+    three runs of columns, each starting at a column of its own (negative: absent, its work is left out).  At ``kv_col``
+    (default: behind the queries): the latent (``rank`` elements, RMS-normed with ``c_norm_w``) and the shared key part
+    (``rdim`` elements, rotated) become the token's key ``[rank + rdim]`` and, where ``v_new`` / ``v_pages`` are given,
+    value ``[rank]`` of ONE key/value head (packed and/or into the cache pages).  At ``q_col``: ``nh (dim + rdim)`` query
+    elements; every head's unrotated part goes to ``q_plain_out`` ``[N, nh, dim]`` and its rotated part, rotated, to the
+    last ``rdim`` elements of ``q_out`` ``[N, nh, rank + rdim]`` (the first ``rank`` are ``head_linear``'s to fill).  At
+    ``cq_col``: a latent of the queries, RMS-normed with ``cq_norm_w`` into ``cq_out`` ``[N, cq_rank]``.  ``pairing``: which
+    elements a rotation pairs, 0 (i, i + rdim / 2) or 1 (2i, 2i + 1)."""
     lib = _lib("latent")
     p_n, n, width = rows.shape
     kd = kv_rank + rot_dim
-    assert width == n_heads * (head_dim + rot_dim) + kd, (width, n_heads, head_dim, rot_dim, kv_rank)
-    assert q_plain_out.shape == (n, n_heads, head_dim) and q_out.shape == (n, n_heads, kd)
-    for t in (q_plain_out, k_new, v_new, k_pages, v_pages):
-        if t is not None and t.dtype != q_out.dtype:
-            raise KernelError("latent_prep: all outputs must share one dtype")
+    qw = n_heads * (head_dim + rot_dim)
+    if kv_col is None:
+        kv_col = qw
+    outs = [t for t in (q_plain_out, q_out, k_new, v_new, k_pages, v_pages, cq_out) if t is not None]
+    if not outs:
+        raise KernelError("latent_prep: nothing to write")
+    dtype = outs[0].dtype
+    if any(t.dtype != dtype for t in outs):
+        raise KernelError("latent_prep: all outputs must share one dtype")
     a = _LatentPrepArgs()
     a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.row_width, a.q_col, a.kv_col, a.cq_col, a.pairing = width, q_col, kv_col, cq_col, pairing
+    if q_col >= 0:
+        assert q_plain_out.shape == (n, n_heads, head_dim) and q_out.shape == (n, n_heads, kd)
+        assert q_plain_out.is_contiguous() and q_out.is_contiguous()
+    if cq_col >= 0:
+        assert cq_out.dim() == 2 and cq_out.shape[0] == n and cq_norm_w.shape == (cq_out.shape[1],) and cq_out.is_contiguous()
+        if cq_norm_w.dtype != c_norm_w.dtype:
+            raise KernelError("latent_prep: both norm weights must share a dtype")
+        a.cq_rank, a.cq_norm_w, a.cq_out = cq_out.shape[1], _ptr(cq_norm_w), _ptr(cq_out)
     a.c_norm_w, a.w_dtype, a.norm_eps = _ptr(c_norm_w), _dt(c_norm_w), float(norm_eps)
     if rot_dim:
         assert cos is not None and cos.shape == sin.shape and cos.shape[1] * 2 == rot_dim
         a.cos_table, a.sin_table, a.table_positions = _ptr(cos, torch.float32), _ptr(sin, torch.float32), cos.shape[0]
     a.positions = _ptr(positions, torch.int32)
-    a.q_plain, a.q_out, a.k_new, a.v_new = _ptr(q_plain_out), _ptr(q_out), _ptr(k_new), _ptr(v_new)
+    a.q_plain, a.q_out = (_ptr(q_plain_out), _ptr(q_out)) if q_col >= 0 else (None, None)
+    a.k_new, a.v_new = _ptr(k_new), _ptr(v_new)
     a.k_pages, a.v_pages = _ptr(k_pages), _ptr(v_pages)
     if k_pages is not None:
         assert k_pages.shape[1] == 1 and k_pages.shape[3] == kd and (v_pages is None or v_pages.shape[3] == kv_rank)
@@ -734,7 +804,96 @@ def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int
     a.ring_pages = ring_pages
     a.seq_of_token, a.slots = _ptr(seq_of_token, torch.int32), _ptr(slots, torch.int32)
     a.n_tokens, a.nh, a.dim, a.rdim, a.rank = n, n_heads, head_dim, rot_dim, kv_rank
-    _check(lib, lib.llg_latent_prep(byref(a), _dt(q_out), _stream()))
+    _check(lib, lib.llg_latent_prep(byref(a), _dtype_code(dtype), _stream()))
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, col0: int, bias: Optional[torch.Tensor] = None) -> None:
+    """x[n, j] *= sigmoid(sum of the partials ``gate[:, n, col0 + j]`` + ``bias[j]``), in place: ``x`` ``[N, W]`` contiguous,
+    ``gate`` float32 partial sums ``[P, N, width]`` of a product whose columns ``col0 .. col0 + W`` are the gate's arguments."""
+    lib = _lib("latent")
+    n, w = x.shape
+    p_n, n2, width = gate.shape
+    assert n2 == n and x.is_contiguous() and (bias is None or bias.shape == (w,))
+    _check(lib, lib.llg_sigmoid_gate(_ptr(x), _dt(x), _ptr(gate, torch.float32), p_n, n * width, width, col0,
+                                     _ptr(bias, torch.float32), n, w, _stream()))
+
+
+NORM_MAX_GROUPS = 64         # groups of a grouped RMS norm; checked against the library at first use
+
+
+def gated_add_group_rmsnorm(residual: torch.Tensor, branch: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                            gate_bias: Optional[torch.Tensor], post_w: Optional[torch.Tensor], post_groups: int,
+                            post_eps: float, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor,
+                            rows: Optional[torch.Tensor] = None) -> None:
+    """RMS norm in groups fused with the residual add.  For output row j (token r = ``rows[j]`` or j), with y the sum of
+    ``branch``'s partials ``[S, N, H]``: ``y *= sigmoid(sum of gate's partials [S', N, H] + gate_bias)`` where ``gate`` is given;
+    ``y = group_rms(y, post_groups, post_eps) * post_w`` where ``post_w`` is given; ``residual[r] += y``;
+    ``out[j] = group_rms(residual[r], groups, eps) * weight``.  ``group_rms`` cuts a row into equal consecutive parts and
+    divides each by the root of (its mean square + eps).  The residual is float32 ``[N, H]``; without a branch the row is
+    only normed."""
+    lib = _lib("groupnorm")
+    n, hidden = residual.shape
+    m = out.shape[0]
+    assert out.shape[1] == hidden and weight.shape == (hidden,) and out.is_contiguous()
+    assert (rows.numel() == m) if rows is not None else (m == n)
+    a = _GroupNormArgs()
+    a.residual = _ptr(residual, torch.float32)
+    a.partial_stride = n * hidden
+    if branch is not None:
+        assert branch.dim() == 3 and branch.shape[1:] == (n, hidden), (branch.shape, residual.shape)
+        a.branch, a.n_partials = _ptr(branch, torch.float32), branch.shape[0]
+        if gate is not None:
+            assert gate.dim() == 3 and gate.shape[1:] == (n, hidden), (gate.shape, residual.shape)
+            assert gate_bias is None or gate_bias.shape == (hidden,)
+            a.gate, a.gate_partials, a.gate_bias = _ptr(gate, torch.float32), gate.shape[0], _ptr(gate_bias, torch.float32)
+        if post_w is not None:
+            assert post_w.shape == (hidden,)
+            if post_w.dtype != weight.dtype:
+                raise KernelError("group_rmsnorm: both norm weights must share a dtype")
+            a.post_w, a.post_groups, a.post_eps = _ptr(post_w), int(post_groups), float(post_eps)
+    elif gate is not None or post_w is not None:
+        raise KernelError("group_rmsnorm: a gate or a norm of the branch needs the branch")
+    a.weight, a.w_dtype, a.groups, a.eps = _ptr(weight), _dt(weight), int(groups), float(eps)
+    a.out, a.out_dtype, a.rows, a.n_out, a.hidden = _ptr(out), _dt(out), _ptr(rows, torch.int32), m, hidden
+    _check(lib, lib.llg_gated_add_group_rmsnorm(byref(a), _stream()))
+
+
+MINGRU_PIECE = 64            # tokens of a piece of the minGRU scan; checked against the library at first use
+
+
+def mingru_pieces(max_count: int) -> int:
+    """Pieces per sequence that ``mingru_scan`` wants a carry for when the longest sequence of a step brings
+    ``max_count`` tokens (1: no carry)."""
+    return max(1, -(-int(max_count) // MINGRU_PIECE))
+
+
+def mingru_scan(rows: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_tokens: torch.Tensor,
+                out: torch.Tensor, carry: Optional[torch.Tensor] = None) -> None:
+    """The minGRU recurrence along every sequence of a step.  ``rows``: float32 partials ``[P, N, 3 size]`` holding the
+    arguments of z | u | g; ``bias`` float32 ``[2 size]`` (of z and u); per channel ``S_t = (1 - z_t) S_{t-1} + z_t c_t``
+    with ``z = sigmoid(.)``, ``c = u + 1/2`` (u >= 0) or ``sigmoid(u)``; ``out[n] = S_t silu(g_t)`` ``[N, size]``.
+    ``state`` float32 ``[slots, size]`` holds S before the step at ``slots[b]`` and receives S after it; sequence b's
+    tokens are ``cu_tokens[b] .. cu_tokens[b + 1]``.  ``carry`` float32 ``[B, pieces, 2, size]``: scratch that lets a long
+    prompt be scanned in pieces side by side (``pieces = mingru_pieces(longest sequence)``); without it every sequence is
+    walked token by token by one thread per channel."""
+    lib = _lib("recurrent")
+    p_n, n, width = rows.shape
+    size = out.shape[1]
+    n_seqs = slots.numel()
+    assert width == 3 * size and out.shape == (n, size) and bias.shape == (2 * size,) and out.is_contiguous()
+    assert state.dim() == 2 and state.shape[1] == size and state.is_contiguous() and cu_tokens.numel() == n_seqs + 1
+    a = _MinGruArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.bias, a.state = _ptr(bias, torch.float32), _ptr(state, torch.float32)
+    a.slots, a.cu_tokens = _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.out, a.out_dtype = _ptr(out), _dt(out)
+    max_count = 0
+    if carry is not None:
+        assert carry.dim() == 4 and carry.shape[0] >= n_seqs and carry.shape[2:] == (2, size) and carry.is_contiguous()
+        a.carry, a.pieces = _ptr(carry, torch.float32), carry.shape[1]
+        max_count = min(n, carry.shape[1] * MINGRU_PIECE)
+    a.n_seqs, a.n_tokens, a.size = n_seqs, n, size
+    _check(lib, lib.llg_mingru_scan(byref(a), max_count, _stream()), kernels=3 if carry is not None else 1)
 
 
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
@@ -798,28 +957,56 @@ def moe_row_capacity(pairs: int, n_experts: int, tile: int = MOE_TILE_ROWS) -> i
     return -(-cap // tile) * tile
 
 
+class RouterRule:
+    """How logits become a token's experts and weights.  ``score`` "softmax": the ``top`` largest logits, weighted by a
+    softmax over them.  "sigmoid": scores ``s = sigmoid(logit)``; with ``groups`` the experts form that many equal groups of
+    neighbours, a group is judged by the sum of its ``group_score_top`` largest scores and only the ``keep_groups`` best
+    groups' experts can be chosen; the ``top`` largest eligible scores, ``weight = s / (sum of the chosen + weight_sum_eps) *
+    weight_scale``."""
+
+    def __init__(self, score: str = "softmax", groups: int = 0, keep_groups: int = 0, group_score_top: int = 2,
+                 weight_scale: float = 1.0, weight_sum_eps: float = 0.0):
+        if score not in ("softmax", "sigmoid"):
+            raise KernelError(f"router rule: score '{score}' is not known (softmax, sigmoid)")
+        self.c = _RouterRule(1 if score == "sigmoid" else 0, int(groups), int(keep_groups), int(group_score_top),
+                             float(weight_scale), float(weight_sum_eps))
+
+
+def _rule_ref(rule: Optional["RouterRule"]):
+    return byref(rule.c) if rule is not None else None
+
+
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor,
-              weight: torch.Tensor) -> None:
+              weight: torch.Tensor, rule: Optional[RouterRule] = None, extra_out: Optional[torch.Tensor] = None) -> None:
     """Per token: ``z = w_router x + b_router`` in float32, ``choice[n]`` the ``top`` experts of largest z (largest
-    first; of equals the lower index), ``weight[n]`` the softmax over those z.  ``w_router`` and ``b_router`` float32."""
+    first; of equals the lower index), ``weight[n]`` the softmax over those z, or what ``rule`` says.  ``w_router`` and
+    ``b_router`` float32.  With ``extra_out`` ``[N]`` the matrix has one more row behind the experts' and ``extra_out[n]``
+    receives the sigmoid of its product with ``x[n]``."""
     lib = _moe_lib()
     n, hidden = x.shape
-    n_exp, top = w_router.shape[0], choice.shape[1]
-    assert w_router.shape == (n_exp, hidden) and choice.shape == (n, top) and weight.shape == (n, top)
+    top = choice.shape[1]
+    n_exp = w_router.shape[0] - (1 if extra_out is not None else 0)
+    assert w_router.shape[1] == hidden and choice.shape == (n, top) and weight.shape == (n, top)
     assert b_router is None or b_router.shape == (n_exp,)
+    assert extra_out is None or extra_out.shape == (n,)
     _check(lib, lib.llg_moe_route(_ptr(x), _dt(x), _ptr(w_router, torch.float32), _ptr(b_router, torch.float32),
-                                  _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, hidden, n_exp, top, _stream()))
+                                  _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, hidden, n_exp, top,
+                                  _rule_ref(rule), _ptr(extra_out, torch.float32), _stream()))
 
 
-def moe_topk(logits: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor) -> None:
-    """As ``moe_route``, from router logits that a product has left as float32 partial sums ``[S, N, experts]``: the
-    partials and the bias are added, then the experts are chosen and weighed."""
+def moe_topk(logits: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
+             rule: Optional[RouterRule] = None, extra_out: Optional[torch.Tensor] = None) -> None:
+    """As ``moe_route``, from router logits that a product has left as float32 partial sums ``[S, N, experts]`` (one more
+    column with ``extra_out``): the partials and the bias are added, then the experts are chosen and weighed."""
     lib = _moe_lib()
-    s, n, n_exp = logits.shape
+    s, n, width = logits.shape
+    n_exp = width - (1 if extra_out is not None else 0)
     top = choice.shape[1]
     assert choice.shape == (n, top) and weight.shape == (n, top) and (b_router is None or b_router.shape == (n_exp,))
-    _check(lib, lib.llg_moe_topk(_ptr(logits, torch.float32), s, n * n_exp, _ptr(b_router, torch.float32),
-                                 _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, n_exp, top, _stream()))
+    assert extra_out is None or extra_out.shape == (n,)
+    _check(lib, lib.llg_moe_topk(_ptr(logits, torch.float32), s, n * width, _ptr(b_router, torch.float32),
+                                 _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, n_exp, top,
+                                 _rule_ref(rule), _ptr(extra_out, torch.float32), _stream()))
 
 
 def moe_plan(choice: torch.Tensor, n_experts: int, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,
@@ -912,8 +1099,9 @@ def moe_down(act: torch.Tensor, tile_expert: torch.Tensor, w_down: torch.Tensor,
 
 
 def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
-    """out[n] = sum_k weight[n, k] y[row_of_pair[n * top + k]] + the sum of ``shared``'s partials ``[S, N, H]`` (if any)."""
+                out: torch.Tensor, shared_scale: Optional[torch.Tensor] = None) -> None:
+    """out[n] = sum_k weight[n, k] y[row_of_pair[n * top + k]] + the sum of ``shared``'s partials ``[S, N, H]`` (if any),
+    that sum times ``shared_scale[n]`` where given (float32 ``[N]``)."""
     lib = _moe_lib()
     n, top = weight.shape
     hidden = y.shape[1]
@@ -922,9 +1110,10 @@ def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, weight: torch.Tensor
     if shared is not None:
         assert shared.dim() == 3 and shared.shape[1:] == (n, hidden)
         n_shared = shared.shape[0]
+    assert shared_scale is None or (shared is not None and shared_scale.shape == (n,))
     _check(lib, lib.llg_moe_combine(_ptr(y, torch.float32), _ptr(row_of_pair, torch.int32), _ptr(weight, torch.float32),
-                                    _ptr(shared, torch.float32), n_shared, n * hidden, _ptr(out, torch.float32), n, hidden,
-                                    top, _stream()))
+                                    _ptr(shared, torch.float32), n_shared, n * hidden, _ptr(shared_scale, torch.float32),
+                                    _ptr(out, torch.float32), n, hidden, top, _stream()))
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
@@ -964,14 +1153,28 @@ def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, 
                                  _ptr(len_before, torch.int32), n, nkv, hd, _dt(k_new), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n, i] = silu(g) * u; the summed partials ``[S, N, gated_rows(I)]`` hold g and u in the gated
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[n, i] = act(g) * u, act = ``activation`` (one of ``GATE_ACTIVATIONS``; silu by default); the summed partials ``[S, N, gated_rows(I)]`` hold g and u in the gated
     layout (g of feature i at i, u at ``gated_rows(I) / 2 + i``)."""
     lib = _lib("elementwise")
     s, n, two_i = gate_up.shape
     inter = out.shape[1]
     assert out.shape == (n, inter) and two_i == gated_rows(inter)
+    if activation != "silu":
+        if activation not in GATE_ACTIVATIONS:
+            raise KernelError(f"silu_mul: gate activation '{activation}' is not known ({', '.join(GATE_ACTIVATIONS)})")
+        _check(lib, lib.llg_gate_mul(_ptr(gate_up), _dt(gate_up), s, n * two_i, _ptr(out), _dt(out), n, inter,
+                                     ACTIVATIONS[activation], _stream()))
+        return
     _check(lib, lib.llg_silu_mul(_ptr(gate_up), _dt(gate_up), s, n * two_i, _ptr(out), _dt(out), n, inter, _stream()))
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap tanh(x / cap) in place (float32, contiguous)."""
+    lib = _lib("elementwise")
+    if not x.is_contiguous():
+        raise KernelError("tanh_cap: the tensor must be contiguous")
+    _check(lib, lib.llg_tanh_cap(_ptr(x, torch.float32), x.numel(), float(cap), _stream()))
 
 
 def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None:
