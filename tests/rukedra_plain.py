@@ -154,11 +154,13 @@ def expert(h, w, p):
 
 
 def route(h, w, p, router: dict):
-    """(chosen experts [T, top], their weights [T, top], by how much the last chosen score beats the best eligible one
-    left out [T]; infinite where every eligible expert is chosen)."""
+    """(chosen experts [T, top], their weights [T, top], margin [T]): the margin is by how much the last chosen score
+    beats the best eligible one left out, or, if less, by how much the last kept group's score beats the best group
+    left out; infinite where nothing is left out."""
     n_exp, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(linear(h, w[p + "router"]))
     eligible = torch.ones_like(s, dtype=torch.bool)
+    margin = torch.full((s.shape[0],), math.inf, dtype=F64)
     groups = router.get("groups")
     if groups:
         count, keep = int(groups["count"]), int(groups["keep"])
@@ -168,12 +170,13 @@ def route(h, w, p, router: dict):
         best = torch.topk(group_score, keep, dim=-1).indices
         ok = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, best, True)
         eligible = ok[:, :, None].expand(-1, -1, per).reshape(-1, n_exp)
+        if keep < count:
+            ordered = torch.sort(group_score, dim=-1, descending=True).values
+            margin = ordered[:, keep - 1] - ordered[:, keep]
     masked = s.masked_fill(~eligible, -1.0)
     val, idx = torch.topk(masked, top, dim=-1)
     if top < int(eligible.sum(-1).min()):
-        margin = val[:, -1] - torch.topk(masked, top + 1, dim=-1).values[:, -1]
-    else:
-        margin = torch.full((s.shape[0],), math.inf, dtype=F64)
+        margin = torch.minimum(margin, val[:, -1] - torch.topk(masked, top + 1, dim=-1).values[:, -1])
     weights = val / (val.sum(-1, keepdim=True) + 1e-20) * float(router.get("scale", 1.0))
     return idx, weights, margin
 
