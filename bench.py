@@ -23,7 +23,9 @@ records the CUDA graphs of its decode steps inside its decode time); the one of 
 ``--probe designs`` prints another line instead: the Karitar design beside the closest stock model (Qwen3) at equal layer
 sizes (``--sizes``), prompt and decode throughput of each and every kernel of the two steps against its roofline;
 ``--design fipavik`` puts the Fipavik design (latent and chunked attention, a mixture of experts whose active size is the
-stock model's feed-forward) in Karitar's place.
+stock model's feed-forward) in Karitar's place; ``--design rukedra`` puts the Rukedra design (two kinds of latent attention
+and a minGRU mixer between grouped norms with gated residuals, dense and mixture feed-forwards in turn) beside Fipavik, the
+closest model the library has, at equal latent, expert and feed-forward sizes.
 """
 import argparse
 import json
@@ -388,6 +390,28 @@ def fipavik_config(size):
             "layers": layers}
 
 
+def rukedra_config(size):
+    """Rukedra at a size, four layers: windowed latent attention with a dense feed-forward, minGRU with a mixture, causal
+    latent attention with a dense feed-forward, windowed latent attention with a mixture.  The latent sizes, the experts
+    (sixteen in four groups of which two stay, four per token, a shared expert) and the window are Fipavik's at this
+    size; the queries' bottleneck is half the width, the recurrent state as wide as the model, the dense feed-forward the
+    stock model's."""
+    width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
+    rot = {"base": 10000.0, "dims": hd // 4, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    lat2 = {"heads": heads, "dim": hd, "rot_dim": hd // 4, "vdim": hd, "kv_rank": 3 * hd // 4, "scale": (hd + hd // 4) ** -0.5, "rot": rot}
+    lat = dict(lat2, q_rank=width // 2, mask={"size": window or 2048})
+    moe = {"kind": "moe", "router": {"experts": FIPAVIK_EXPERTS, "top": FIPAVIK_TOP, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": ff // 8}, "shared": {"ff": ff // 2}}
+    dense = {"kind": "dense", "ff": ff}
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(dense)},
+              {"type": "mingru", "mixer": {"width": width}, "mlp": dict(moe)},
+              {"type": "latent_attention_2", "mixer": dict(lat2), "mlp": dict(dense)},
+              {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(moe)}]
+    assert len(layers) == DESIGN_LAYERS
+    return {"architecture": "Rukedra", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6, "groups": 2},
+            "logit_softcap": 30.0, "layers": layers}
+
+
 def design_configs(size, design="karitar"):
     """The configuration of ``design`` (Karitar or Fipavik) at a size and the closest stock model's (Qwen3: grouped-query
     attention with normed queries and keys and the same window, pre-norm blocks) with the same width, heads, head size
@@ -406,12 +430,15 @@ def design_configs(size, design="karitar"):
         qwen3.update(sliding_window=window, layer_types=["sliding_attention"] * DESIGN_LAYERS)
     if design == "fipavik":
         return {"fipavik": fipavik_config(size), "qwen3": qwen3}
+    if design == "rukedra":
+        return {"rukedra": rukedra_config(size), "fipavik": fipavik_config(size)}
     return {"karitar": karitar, "qwen3": qwen3}
 
 
 _TIMED_OPS = ("embed_rows", "add_rmsnorm", "hc_add_rmsnorm", "qk_prep", "qkv_row_prep", "gemm_tc", "gemm_tc_act", "gemm_tc_qkv",
               "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write", "add_layernorm", "latent_prep", "head_linear",
-              "moe_route", "moe_topk", "moe_plan", "moe_gather_rows", "moe_gated", "moe_down", "moe_combine")
+              "moe_route", "moe_topk", "moe_plan", "moe_gather_rows", "moe_gated", "moe_down", "moe_combine",
+              "gated_add_group_rmsnorm", "mingru_scan", "sigmoid_gate", "tanh_cap")
 
 
 def _kernel_label(name, args, kw):
@@ -451,6 +478,22 @@ def _kernel_cost(name, args, kw, keys_read):
         residual, parts, out = args[0], args[1], args[6]
         m, h = out.shape
         return m * (4 * h * (2 if parts else 1) + 4 * h * sum(p.shape[0] for p in parts) + h * out.element_size()), 0.0
+    if name == "gated_add_group_rmsnorm":
+        # per normalised row: the residual read (and written back with a branch), the branch's and the gate's partial sums,
+        # the output row
+        branch, gate, out = args[1], args[2], args[10]
+        m, h = out.shape
+        per_row = 4 * h * (2 if branch is not None else 1) + 4 * h * sum(t.shape[0] for t in (branch, gate) if t is not None)
+        return m * (per_row + h * out.element_size()), 0.0
+    if name == "sigmoid_gate":
+        x, gate = args[0], args[1]
+        return 2 * x.nbytes + gate.shape[0] * x.numel() * 4, 0.0
+    if name == "tanh_cap":
+        return 2 * args[0].nbytes, 0.0
+    if name == "mingru_scan":
+        # the input product's partial sums and the outputs; with the scan in pieces the sums are read twice
+        rows, out, carry = args[0], args[5], args[6] if len(args) > 6 else kw.get("carry")
+        return rows.nbytes * (2 if carry is not None else 1) + out.nbytes, 0.0
     if name in ("moe_gated", "moe_down"):
         # the pairs' rows (the layout's filling rows left out) against the matrices of the experts they can reach
         w = args[3] if name == "moe_gated" else args[2]
@@ -600,7 +643,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --probe timeline: the time line of a prompt step of so many tokens instead of a decode step")
     ap.add_argument("--sizes", default=",".join(DESIGN_SIZES), help="with --probe designs: which of " + ", ".join(DESIGN_SIZES))
-    ap.add_argument("--design", choices=["karitar", "fipavik"], default="karitar",
+    ap.add_argument("--design", choices=["karitar", "fipavik", "rukedra"], default="karitar",
                     help="with --probe designs: the design that stands beside the closest stock model")
     ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline", "designs"],
                     help="instead of the bench line, print a table: decode attention alone over batch shapes; what "

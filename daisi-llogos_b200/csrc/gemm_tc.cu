@@ -125,10 +125,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-// What the gate of a gated epilogue passes: act 0 silu, else kind act - 1 of llg_act (common.cuh).  The choice is the
-// same for every element of a launch.
-__device__ __forceinline__ float gate_act(int act, float g) {
-  return act == 0 ? __fdividef(g, 1.0f + __expf(-g)) : llg_act(act - 1, g);
+// What the gate of a gated epilogue passes: g sigmoid(g (a + b g^2)).  (a, b) = (1, 0) is silu; the tanh form of gelu,
+// 0.5 g (1 + tanh(c (g + 0.044715 g^3))), is the same as g sigmoid(2 c (g + 0.044715 g^3)), so (a, b) = (2 c, 2 c 0.044715)
+// with c = sqrt(2 / pi).  One form without a branch: the epilogue of every gated product costs what silu's did.
+#define LLG_GELU_GATE_A 1.5957691216057308f
+#define LLG_GELU_GATE_B 0.07135481627260025f
+__device__ __forceinline__ float gate_act(float a, float b, float g) {
+  return __fdividef(g, 1.0f + __expf(-g * fmaf(b * g, g, a)));
 }
 
 struct GemmParams {
@@ -142,7 +145,7 @@ struct GemmParams {
   RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
   int act;          // EPI -1 (the plain epilogue with an activation; one split): kind + 1, every element goes through
                     // llg_act(kind, .) before it is stored.  A variant of its own, so that the plain products carry none of it.
-                    // EPI 1 (the gated epilogue): 0 = the gate passes silu, else kind + 1 of the gate's activation.
+                    // EPI 1 (the gated epilogue): 0 = the gate passes silu, else the tanh form of gelu.
   // Grouped products (SWAP 1, one token tile per block): token tile t multiplies with the matrix of group tile_group[t],
   // whose rows start at row tile_group[t] * group_rows of w; a tile whose group is negative is left out by every role.
   // The list is written by a kernel earlier in the step, so nothing of w is requested ahead of the dependency wait.
@@ -415,6 +418,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   } else {
     // ---- epilogue: warps 0-3, each its quarter of the lanes: tensor memory -> registers -> out ----------------------
     pdl_wait();                 // before anything of the previous kernel is read or overwritten
+    const float gate_a = EPI == 1 && p.act ? LLG_GELU_GATE_A : 1.0f, gate_b = EPI == 1 && p.act ? LLG_GELU_GATE_B : 0.0f;
     int round = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
       if (grouped && group_of(tile) < 0) { --round; continue; }
@@ -548,7 +552,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                   const float g = __uint_as_float(r[c]) * rs;
-                  v[c] = gate_act(p.act, g) * (__uint_as_float(ru[c]) * rs);
+                  v[c] = gate_act(gate_a, gate_b, g) * (__uint_as_float(ru[c]) * rs);
                 }
               } else {
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -647,7 +651,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 for (int c = 0; c < 16; ++c) {
                   const float rs = p.scale.ss ? col_scale[c0 + 16 * q + c] : 1.0f;
                   const float g = __uint_as_float(rg[q][c]) * rs, u = __uint_as_float(ru[q][c]) * rs;
-                  v[c] = gate_act(p.act, g) * u;
+                  v[c] = gate_act(gate_a, gate_b, g) * u;
                 }
                 OT* dst = out + (long long)(n0 + c0 + 16 * q) * inter + f;
   #pragma unroll
@@ -781,8 +785,8 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
 // act(gate) * up, kind as in llg_act (common.cuh).
 LLG_API int llg_gemm_tc_gated(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int tile_n,
                               int gated_features, int kind, const RowScale* scale, cudaStream_t stream) {
-  LLG_REQUIRE(kind >= 0 && kind < LLG_ACT_KINDS && gated_features > 0, "gemm_tc_gated: activation kind %d, %d features", kind,
-              gated_features);
+  LLG_REQUIRE((kind == 1 || kind == 2) && gated_features > 0, "gemm_tc_gated: activation kind %d (1 gelu, 2 silu), %d features",
+              kind, gated_features);
   return gemm_tc_run(x, w, out, out_dtype, n, o, k, 1, tile_n, gated_features, scale, kind == 2 ? 0 : kind + 1, stream);
 }
 

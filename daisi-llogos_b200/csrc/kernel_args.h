@@ -233,7 +233,7 @@ struct LayerNormArgs {
 //   v  = residual[r] + y                                      (written back where branch is given)
 //   out[j] = group_rms(v, groups, eps) * weight
 // group_rms(v, g, e): v in g equal consecutive parts, each divided by sqrt(mean(part^2) + e).
-#define LLG_NORM_MAX_GROUPS 64
+#define LLG_NORM_MAX_GROUPS 65536
 struct GroupNormArgs {
   float* residual;            // [n_tokens][hidden]
   const float* branch;        // [n_partials][n_tokens][hidden] or null

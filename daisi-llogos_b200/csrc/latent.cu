@@ -18,15 +18,93 @@ LLG_API const char* llg_last_error() { return g_llg_error; }
 
 namespace {
 
-// One warp per unit of a token.  The units a launch has, in this order: the nh query heads (q_col >= 0), the latent with
-// the shared key part (kv_col >= 0), the queries' latent (cq_col >= 0).
+// Four neighbouring elements at once (the callers' hosts check sizes and addresses).
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const unsigned int*>(&lo);
+  t.y = *reinterpret_cast<const unsigned int*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// The queries' latent of token n: RMS norm over its cq_rank elements by a whole block (the latent is as long as a good
+// part of the model's width).  Each thread adds the partial sums of its elements, four neighbours at a time where the
+// host found that the sizes and addresses allow it (vec), once for the sum of squares and once more for the output.
 template <typename OT, typename WT>
-__global__ void latent_prep_kernel(LatentPrepArgs a) {
+__device__ __forceinline__ void query_latent_norm(const LatentPrepArgs& a, int n, int vec) {
+  __shared__ float scratch[32];
+  const float* src = a.rows + (long long)n * a.row_width + a.cq_col;
+  const WT* w = (const WT*)a.cq_norm_w;
+  OT* o = (OT*)a.cq_out + (long long)n * a.cq_rank;
+  float ss = 0.f;
+  if (vec) {
+    auto sum4 = [&](int d, float (&v)[4]) {
+      load4(src + d, v);
+      float t[4];
+#pragma unroll 4
+      for (int s = 1; s < a.n_partials; ++s) {
+        load4(src + s * a.partial_stride + d, t);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] += t[c];
+      }
+    };
+    float v[4], ww[4];
+    for (int d = threadIdx.x * 4; d < a.cq_rank; d += blockDim.x * 4) {
+      sum4(d, v);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ss = fmaf(v[c], v[c], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)a.cq_rank + a.norm_eps);
+    for (int d = threadIdx.x * 4; d < a.cq_rank; d += blockDim.x * 4) {
+      sum4(d, v);
+      load4(w + d, ww);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = v[c] * inv * ww[c];
+      store4(o + d, v);
+    }
+    return;
+  }
+  auto summed = [&](int d) {
+    float v = 0.f;
+    for (int s = 0; s < a.n_partials; ++s) v += src[s * a.partial_stride + d];
+    return v;
+  };
+  for (int d = threadIdx.x; d < a.cq_rank; d += blockDim.x) {
+    const float v = summed(d);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)a.cq_rank + a.norm_eps);
+  for (int d = threadIdx.x; d < a.cq_rank; d += blockDim.x) o[d] = from_f32<OT>(summed(d) * inv * to_f32(w[d]));
+}
+
+// One warp per unit of a token.  The units a launch has, in this order: the nh query heads (q_col >= 0), the latent with
+// the shared key part (kv_col >= 0).  The blocks behind the units' (unit_blocks of them) take the queries' latent
+// (cq_col >= 0), one block a token.
+template <typename OT, typename WT>
+__global__ void latent_prep_kernel(LatentPrepArgs a, int unit_blocks, int cq_vec) {
   pdl_launch_dependents();
   pdl_wait();
+  if ((int)blockIdx.x >= unit_blocks) {
+    query_latent_norm<OT, WT>(a, (int)blockIdx.x - unit_blocks, cq_vec);
+    return;
+  }
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_units = a.q_col >= 0 ? a.nh : 0, kv_units = a.kv_col >= 0 ? 1 : 0;
-  const int units = q_units + kv_units + (a.cq_col >= 0 ? 1 : 0);
+  const int units = q_units + kv_units;
   const long long item = (long long)blockIdx.x * warps + warp;
   if (item >= (long long)a.n_tokens * units) return;
   const int n = (int)(item / units), u = (int)(item % units);
@@ -56,20 +134,7 @@ __global__ void latent_prep_kernel(LatentPrepArgs a) {
     }
     return;
   }
-  const WT* w = (const WT*)(u < q_units + kv_units ? a.c_norm_w : a.cq_norm_w);
-  if (u >= q_units + kv_units) {
-    // the queries' latent: RMS norm over its cq_rank elements
-    float ss = 0.f;
-    for (int d = lane; d < a.cq_rank; d += 32) {
-      const float v = summed(a.cq_col + d);
-      ss += v * v;
-    }
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)a.cq_rank + a.norm_eps);
-    OT* o = (OT*)a.cq_out + (long long)n * a.cq_rank;
-    for (int d = lane; d < a.cq_rank; d += 32) o[d] = from_f32<OT>(summed(a.cq_col + d) * inv * to_f32(w[d]));
-    return;
-  }
+  const WT* w = (const WT*)a.c_norm_w;
   // the latent: RMS norm over its kv_rank elements
   const long long col = a.kv_col;
   float ss = 0.f;
@@ -119,6 +184,36 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__
   float z = bias ? bias[j] : 0.f;
   for (int s = 0; s < n_partials; ++s) z += g[s * partial_stride];
   x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-z)));
+}
+
+// The same, four neighbouring elements of a row per thread (the host checks that rows, columns and addresses allow it).
+template <typename T>
+__global__ void sigmoid_gate4_kernel(T* __restrict__ x, const float* __restrict__ gate, int n_partials, long long partial_stride,
+                                     int gate_width, int col0, const float* __restrict__ bias, long long total, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= total) return;
+  const long long n = i / width;
+  const int j = (int)(i % width);
+  const float* g = gate + n * gate_width + col0 + j;
+  float z[4], t[4], v[4];
+  load4(g, z);
+#pragma unroll 4
+  for (int s = 1; s < n_partials; ++s) {
+    load4(g + s * partial_stride, t);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) z[c] += t[c];
+  }
+  if (bias) {
+    load4(bias + j, t);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) z[c] += t[c];
+  }
+  load4(x + i, v);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) v[c] = v[c] / (1.0f + expf(-z[c]));
+  store4(x + i, v);
 }
 
 // y[n][h][o] = sum_k w[h][o][k] x[n][h][k].  A block takes TN tokens of one head and TO outputs; x's tile lies in shared
@@ -190,16 +285,21 @@ LLG_API int llg_latent_prep(const LatentPrepArgs* args, int out_dtype, cudaStrea
   LLG_REQUIRE((!a.v_new || a.k_new) && (!a.v_pages || a.k_pages), "latent_prep: values are written beside keys only");
   if (a.n_tokens == 0) return 0;
   const int warps = 4;
-  const long long items = (long long)a.n_tokens * ((a.q_col >= 0 ? a.nh : 0) + (a.kv_col >= 0 ? 1 : 0) + (a.cq_col >= 0 ? 1 : 0));
-  if (items == 0) return 0;
-  const unsigned grid = (unsigned)((items + warps - 1) / warps);
+  const long long items = (long long)a.n_tokens * ((a.q_col >= 0 ? a.nh : 0) + (a.kv_col >= 0 ? 1 : 0));
+  const int unit_blocks = (int)((items + warps - 1) / warps);
+  const int cq_vec = a.cq_col >= 0 && a.cq_col % 4 == 0 && a.cq_rank % 4 == 0 && a.row_width % 4 == 0 && a.partial_stride % 4 == 0 &&
+             (size_t)a.rows % 16 == 0 && (size_t)a.cq_norm_w % 16 == 0 && (size_t)a.cq_out % 16 == 0;
+  const long long blocks = (long long)unit_blocks + (a.cq_col >= 0 ? a.n_tokens : 0);
+  if (blocks == 0) return 0;
+  LLG_REQUIRE(blocks < 2147483647LL, "latent_prep: too many blocks");
+  const unsigned grid = (unsigned)blocks;
   const bool wb = a.w_dtype == LLG_BF16;
   if (out_dtype == LLG_F32) {
-    if (wb) llg_launch(latent_prep_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a);
-    else llg_launch(latent_prep_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, stream, a);
+    if (wb) llg_launch(latent_prep_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a, unit_blocks, cq_vec);
+    else llg_launch(latent_prep_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, stream, a, unit_blocks, cq_vec);
   } else if (out_dtype == LLG_BF16) {
-    if (wb) llg_launch(latent_prep_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a);
-    else llg_launch(latent_prep_kernel<__nv_bfloat16, float>, dim3(grid), dim3(warps * 32), 0, stream, a);
+    if (wb) llg_launch(latent_prep_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a, unit_blocks, cq_vec);
+    else llg_launch(latent_prep_kernel<__nv_bfloat16, float>, dim3(grid), dim3(warps * 32), 0, stream, a, unit_blocks, cq_vec);
   } else {
     return llg_fail("latent_prep: unknown output dtype %d", out_dtype);
   }
@@ -225,13 +325,19 @@ LLG_API int llg_sigmoid_gate(void* x, int dtype, const float* gate, int n_partia
               "sigmoid_gate: bad sizes (width %d at column %d of %d)", width, col0, gate_width);
   if (n_tokens == 0) return 0;
   const long long total = (long long)n_tokens * width;
-  const unsigned grid = (unsigned)((total + 255) / 256);
-  if (dtype == LLG_F32)
-    llg_launch(sigmoid_gate_kernel<float>, dim3(grid), dim3(256), 0, stream, (float*)x, gate, n_partials, partial_stride,
-               gate_width, col0, bias, total, width);
-  else if (dtype == LLG_BF16)
-    llg_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)x, gate, n_partials,
-               partial_stride, gate_width, col0, bias, total, width);
+  const bool vec = width % 4 == 0 && col0 % 4 == 0 && gate_width % 4 == 0 && partial_stride % 4 == 0 && (size_t)x % 16 == 0 &&
+                   (size_t)gate % 16 == 0 && (size_t)bias % 16 == 0;
+  const unsigned grid = (unsigned)(((vec ? total / 4 : total) + 255) / 256);
+#define GATE(T)                                                                                                          \
+  do {                                                                                                                   \
+    if (vec) llg_launch(sigmoid_gate4_kernel<T>, dim3(grid), dim3(256), 0, stream, (T*)x, gate, n_partials, partial_stride, \
+                        gate_width, col0, bias, total, width);                                                           \
+    else llg_launch(sigmoid_gate_kernel<T>, dim3(grid), dim3(256), 0, stream, (T*)x, gate, n_partials, partial_stride,   \
+                    gate_width, col0, bias, total, width);                                                               \
+  } while (0)
+  if (dtype == LLG_F32) GATE(float);
+  else if (dtype == LLG_BF16) GATE(__nv_bfloat16);
+#undef GATE
   else return llg_fail("sigmoid_gate: unknown dtype %d", dtype);
   return llg_check_launch("sigmoid_gate");
 }

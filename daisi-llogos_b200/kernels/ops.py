@@ -818,7 +818,7 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, col0: int, bias: Optional[
                                      _ptr(bias, torch.float32), n, w, _stream()))
 
 
-NORM_MAX_GROUPS = 64         # groups of a grouped RMS norm; checked against the library at first use
+NORM_MAX_GROUPS = 65536      # groups of a grouped RMS norm; checked against the library at first use
 
 
 def gated_add_group_rmsnorm(residual: torch.Tensor, branch: Optional[torch.Tensor], gate: Optional[torch.Tensor],

@@ -169,7 +169,7 @@ def sigmoid_gate(x, gate, col0, bias=None):
     x.copy_((x.float() * torch.sigmoid(z)).to(x.dtype))
 
 
-NORM_MAX_GROUPS = 64
+NORM_MAX_GROUPS = 65536
 
 
 def gated_add_group_rmsnorm(residual, branch, gate, gate_bias, post_w, post_groups, post_eps, weight, groups, eps, out,

@@ -37,6 +37,8 @@ def close(got, ref, dtype, what=(), tol=TOL):
     per_position = (got - ref).pow(2).mean(-1).sqrt() / ref.pow(2).mean().sqrt()
     rms, mean = float(per_position.max()), float(per_position.mean())
     worst = float((got - ref).abs().max() / ref.abs().max())
+    if per_position.numel() < 16:           # an average of a few positions is no average: the per-position bound stands alone
+        mean_tol = rms_tol
     assert rms <= rms_tol and mean <= mean_tol and worst <= max_tol, (*what, "rms", rms, "mean", mean, "max", worst)
 
 
