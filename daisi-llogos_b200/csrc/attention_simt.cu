@@ -1,5 +1,5 @@
 // Attention over the paged key/value cache on the CUDA cores, in float32 arithmetic, for
-// float32 and bfloat16 storage and any head size up to 256.  These kernels are the true
+// float32 and bfloat16 storage and any head size up to 384.  These kernels are the true
 // 32-bit path and the reference the tensor-core kernels are checked against.
 //
 //   attn_prefill : a step that brings several tokens per sequence.  Keys of positions that the
@@ -24,10 +24,14 @@ LLG_API const char* llg_last_error() { return g_llg_error; }
 namespace {
 
 constexpr int KT = 32;      // keys per tile (one per lane)
-constexpr int MAXD = 8;     // head_dim / 32 rounded up, at most
+// head_dim / 32 rounded up, at most: a template parameter of the kernels (MAXD), since the accumulators are registers and
+// every loop over them runs to the bound.  Heads of up to 256 elements take the small form, longer ones (latent
+// attention's keys: a latent and a rotated part) the large one, which ends where a decode block's key tiles fill
+// shared memory.
+constexpr int MAXD_SMALL = 8, MAXD_LARGE = 12;
 constexpr int BQ = 16;      // queries per block in attn_prefill (4 per warp)
 
-template <typename T>
+template <typename T, int MAXD>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   extern __shared__ float sm[];
   __shared__ long long src_off[KT];
@@ -163,7 +167,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 
 constexpr int GC = 8;  // query heads of one key/value head handled per pass
 
-template <typename T>
+template <typename T, int MAXD>
 __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   extern __shared__ float sm[];
   const int hd = a.hd, vd = a.vd > 0 ? a.vd : a.hd;
@@ -330,26 +334,31 @@ LLG_API int llg_attn_prefill_simt(const PrefillArgs* args, int dtype, cudaStream
   const PrefillArgs& a = *args;
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_prefill: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
-  LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD, "attn_prefill: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD);
-  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD, "attn_prefill: value head size %d is outside [1, %d]", a.vd, 32 * MAXD);
+  LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD_LARGE, "attn_prefill: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD_LARGE);
+  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD_LARGE, "attn_prefill: value head size %d is outside [1, %d]", a.vd, 32 * MAXD_LARGE);
   const int vd = a.vd > 0 ? a.vd : a.hd;
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill: bad cache geometry");
   LLG_REQUIRE(a.nh <= 65535, "attn_prefill: too many heads");
   if (a.n_tiles <= 0) return 0;
   const size_t smem = (size_t)(BQ * a.hd + KT * (a.hd + 1) + KT * vd + BQ * KT) * sizeof(float);
   dim3 grid(a.n_tiles, a.nh);
-  cudaError_t e;
+  const bool large = a.hd > 32 * MAXD_SMALL || vd > 32 * MAXD_SMALL;
+#define PREFILL(T, D)                                                                                                   \
+  do {                                                                                                                  \
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess) return llg_fail("attn_prefill: shared memory %zu: %s", smem, cudaGetErrorString(e));          \
+    attn_prefill_kernel<T, D><<<grid, 128, smem, stream>>>(a);                                                          \
+  } while (0)
   if (dtype == LLG_F32) {
-    e = cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return llg_fail("attn_prefill: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    attn_prefill_kernel<float><<<grid, 128, smem, stream>>>(a);
+    if (large) PREFILL(float, MAXD_LARGE);
+    else PREFILL(float, MAXD_SMALL);
   } else if (dtype == LLG_BF16) {
-    e = cudaFuncSetAttribute(attn_prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return llg_fail("attn_prefill: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    attn_prefill_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(a);
+    if (large) PREFILL(__nv_bfloat16, MAXD_LARGE);
+    else PREFILL(__nv_bfloat16, MAXD_SMALL);
   } else {
     return llg_fail("attn_prefill: unknown dtype %d", dtype);
   }
+#undef PREFILL
   return llg_check_launch("attn_prefill");
 }
 
@@ -362,8 +371,8 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
   const DecodeArgs& a = *args;
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_decode: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
-  LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD, "attn_decode: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD);
-  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD, "attn_decode: value head size %d is outside [1, %d]", a.vd, 32 * MAXD);
+  LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD_LARGE, "attn_decode: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD_LARGE);
+  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD_LARGE, "attn_decode: value head size %d is outside [1, %d]", a.vd, 32 * MAXD_LARGE);
   const int vd = a.vd > 0 ? a.vd : a.hd;
   LLG_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535, "attn_decode: n_splits %d", a.n_splits);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode: bad cache geometry");
@@ -376,22 +385,26 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
   const size_t smem = floats * sizeof(float);
   dim3 grid(a.n_splits, a.nkv, a.n_seqs);
   dim3 rgrid(a.nh, a.n_seqs);
-  cudaError_t e;
+  LLG_REQUIRE(smem <= 227 * 1024, "attn_decode: heads of %d elements do not fit shared memory", a.hd);
+  const bool large = a.hd > 32 * MAXD_SMALL || vd > 32 * MAXD_SMALL;
+#define DECODE(T, D)                                                                                                    \
+  do {                                                                                                                  \
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));           \
+    attn_decode_kernel<T, D><<<grid, 128, smem, stream>>>(a);                                                           \
+    attn_decode_reduce_kernel<T><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (T*)out, a.nh, vd, a.n_splits,          \
+                                                          a.has_sink, a.sink_score, a.gate, a.sinks);                  \
+  } while (0)
   if (dtype == LLG_F32) {
-    e = cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    attn_decode_kernel<float><<<grid, 128, smem, stream>>>(a);
-    attn_decode_reduce_kernel<float><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (float*)out, a.nh, vd, a.n_splits,
-                                                               a.has_sink, a.sink_score, a.gate, a.sinks);
+    if (large) DECODE(float, MAXD_LARGE);
+    else DECODE(float, MAXD_SMALL);
   } else if (dtype == LLG_BF16) {
-    e = cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    attn_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(a);
-    attn_decode_reduce_kernel<__nv_bfloat16><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (__nv_bfloat16*)out, a.nh, vd,
-                                                                        a.n_splits, a.has_sink, a.sink_score, a.gate, a.sinks);
+    if (large) DECODE(__nv_bfloat16, MAXD_LARGE);
+    else DECODE(__nv_bfloat16, MAXD_SMALL);
   } else {
     return llg_fail("attn_decode: unknown dtype %d", dtype);
   }
+#undef DECODE
   return llg_check_launch("attn_decode");
 }
 

@@ -89,7 +89,7 @@ __device__ __forceinline__ void group_rms(float* row, int hidden, int groups, fl
 }
 
 template <int VEC, typename OT, typename WT>
-__global__ void __launch_bounds__(1024) gated_add_group_rmsnorm_kernel(GroupNormArgs a) {
+__global__ void __launch_bounds__(1024) gated_add_group_rmsnorm_kernel(GroupNormArgs a, int early_residual) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float row[];
@@ -98,10 +98,14 @@ __global__ void __launch_bounds__(1024) gated_add_group_rmsnorm_kernel(GroupNorm
   const int r = a.rows ? a.rows[j] : j;
   const int hidden = a.hidden;
   float* res = a.residual + (long long)r * hidden;
+  // early_residual: a second row of shared memory takes the residual while the branch is read, so that the add after the
+  // branch's norm does not wait for memory once more
+  float* res_row = early_residual ? row + hidden : nullptr;
   if (a.branch) {
     const float* bp = a.branch + (long long)r * hidden;
     const float* gp = a.gate ? a.gate + (long long)r * hidden : nullptr;
     for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+      if (res_row) store<VEC>(res_row + i, load_f32<VEC>(res + i));
       Pack<VEC> y = load_f32<VEC>(bp + i);
 #pragma unroll 4
       for (int s = 1; s < a.n_partials; ++s) {
@@ -130,7 +134,7 @@ __global__ void __launch_bounds__(1024) gated_add_group_rmsnorm_kernel(GroupNorm
     __syncthreads();
     if (a.post_w) group_rms<VEC, WT, float>(row, hidden, a.post_groups, a.post_eps, (const WT*)a.post_w, nullptr, part);
     for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
-      Pack<VEC> v = load_f32<VEC>(res + i);
+      Pack<VEC> v = load_f32<VEC>(res_row ? res_row + i : res + i);
       const Pack<VEC> y = load_f32<VEC>(row + i);
 #pragma unroll
       for (int c = 0; c < VEC; ++c) v.v[c] += y.v[c];
@@ -167,9 +171,12 @@ LLG_API int llg_gated_add_group_rmsnorm(const GroupNormArgs* args, cudaStream_t 
                    aligned(a.gate, 16) && aligned(a.gate_bias, 16) && aligned(a.post_w, 16) && aligned(a.weight, 16) && aligned(a.out, 16);
   const int per_thread = vec ? 4 : 1;
   int threads = ((a.hidden + per_thread - 1) / per_thread + 31) / 32 * 32;
-  threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
-  const size_t smem = (size_t)a.hidden * sizeof(float);
-  LLG_REQUIRE(smem <= 200 * 1024, "group_rmsnorm: rows of %d elements do not fit shared memory", a.hidden);
+  // many rows: blocks of 512 threads at most, so that an SM holds several rows at different stages
+  const int most = a.n_out > 2 * llg_sm_count() ? 512 : 1024;
+  threads = threads < 128 ? 128 : (threads > most ? most : threads);
+  LLG_REQUIRE((size_t)a.hidden * sizeof(float) <= 200 * 1024, "group_rmsnorm: rows of %d elements do not fit shared memory", a.hidden);
+  const int early_residual = a.branch && (size_t)a.hidden * sizeof(float) <= 48 * 1024;
+  const size_t smem = (size_t)a.hidden * sizeof(float) * (early_residual ? 2 : 1);
 #define LAUNCH_V(V, OT, WT)                                                                                     \
   do {                                                                                                          \
     auto k = gated_add_group_rmsnorm_kernel<V, OT, WT>;                                                         \
@@ -177,7 +184,7 @@ LLG_API int llg_gated_add_group_rmsnorm(const GroupNormArgs* args, cudaStream_t 
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
       if (e != cudaSuccess) return llg_fail("group_rmsnorm: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
     }                                                                                                           \
-    llg_launch(k, dim3(a.n_out), dim3(threads), smem, stream, a);                                               \
+    llg_launch(k, dim3(a.n_out), dim3(threads), smem, stream, a, early_residual);                                              \
   } while (0)
 #define LAUNCH(OT, WT)                      \
   do {                                      \

@@ -17,30 +17,13 @@ namespace {
 // 1 / (1 + exp(-v)) with the correctly rounded reciprocal: the same float as the division gives, in fewer instructions
 __device__ __forceinline__ float sigmoid_f(float v) { return __frcp_rn(1.0f + expf(-v)); }
 
-struct Token {
-  float z, c, g;
-};
-
-// gate z, candidate c and (WITH_G) output-gate argument g of channel ch at token n
-template <bool WITH_G>
-__device__ __forceinline__ Token mingru_token(const MinGruArgs& a, long long n, int ch, float bz, float bu) {
-  const float* p = a.rows + n * (3LL * a.size) + ch;
-  float z = bz, u = bu, g = 0.f;
-  for (int s = 0; s < a.n_partials; ++s) {
-    z += p[s * a.partial_stride];
-    u += p[s * a.partial_stride + a.size];
-    if (WITH_G) g += p[s * a.partial_stride + 2 * a.size];
-  }
-  Token t;
-  t.z = sigmoid_f(z);
-  t.c = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-  t.g = g;
-  return t;
-}
+constexpr int SCAN_BATCH = 8;      // tokens (or pieces) whose loads are issued together, ahead of the arithmetic and the stores
 
 // MODE 0: the whole sequence from state[slot], outputs and the last state written (no carry).
 // MODE 1: a piece from zero; writes (product of 1 - z, state reached) to carry.
 // MODE 2: a piece from carry's starting state; writes outputs.
+// The arguments of SCAN_BATCH tokens are summed from the partials into registers first: the loads of a batch do not wait
+// for one another nor for the stores of the tokens before them, which is what bounds a walk along a sequence.
 template <typename OT, int MODE>
 __global__ void __launch_bounds__(128) mingru_scan_kernel(MinGruArgs a) {
   pdl_launch_dependents();
@@ -65,12 +48,32 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(MinGruArgs a) {
     S = cr[a.size];
   }
   OT* out = (OT*)a.out;
-#pragma unroll 4
-  for (int n = lo; n < hi; ++n) {
-    const Token t = mingru_token<MODE != 1>(a, n, ch, bz, bu);
-    S = (1.0f - t.z) * S + t.z * t.c;
-    if (MODE == 1) A *= 1.0f - t.z;
-    else out[(long long)n * a.size + ch] = from_f32<OT>(S * (t.g * sigmoid_f(t.g)));
+  const long long row = 3LL * a.size;
+  for (int n0 = lo; n0 < hi; n0 += SCAN_BATCH) {
+    float z[SCAN_BATCH], u[SCAN_BATCH], g[SCAN_BATCH];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) { z[k] = bz; u[k] = bu; g[k] = 0.f; }
+    for (int s = 0; s < a.n_partials; ++s) {
+      const float* p = a.rows + s * a.partial_stride + n0 * row + ch;
+#pragma unroll
+      for (int k = 0; k < SCAN_BATCH; ++k) {
+        if (n0 + k < hi) {
+          z[k] += p[k * row];
+          u[k] += p[k * row + a.size];
+          if (MODE != 1) g[k] += p[k * row + 2 * a.size];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (n0 + k < hi) {
+        const float zt = sigmoid_f(z[k]);
+        const float ct = u[k] >= 0.f ? u[k] + 0.5f : sigmoid_f(u[k]);
+        S = (1.0f - zt) * S + zt * ct;
+        if (MODE == 1) A *= 1.0f - zt;
+        else out[(long long)(n0 + k) * a.size + ch] = from_f32<OT>(S * (g[k] * sigmoid_f(g[k])));
+      }
+    }
   }
   if (MODE == 0) a.state[(long long)a.slots[b] * a.size + ch] = S;
   if (MODE == 1) {
@@ -89,10 +92,23 @@ __global__ void __launch_bounds__(128) mingru_join_kernel(MinGruArgs a) {
   float* st = a.state + (long long)a.slots[b] * a.size + ch;
   float S = *st;
   float* cr = a.carry + ((long long)b * a.pieces * 2) * a.size + ch;
-  for (int p = 0; p < a.pieces; ++p, cr += 2LL * a.size) {
-    const float A = cr[0], B = cr[a.size];
-    cr[a.size] = S;
-    S = A * S + B;
+  const long long step = 2LL * a.size;
+  for (int p0 = 0; p0 < a.pieces; p0 += SCAN_BATCH, cr += SCAN_BATCH * step) {
+    float A[SCAN_BATCH], B[SCAN_BATCH];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (p0 + k < a.pieces) {
+        A[k] = cr[k * step];
+        B[k] = cr[k * step + a.size];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (p0 + k < a.pieces) {
+        cr[k * step + a.size] = S;
+        S = A[k] * S + B[k];
+      }
+    }
   }
   *st = S;
 }
