@@ -711,12 +711,12 @@ def test_products_apply_a_row_scale(ops, n, o, k, parts):
 
 
 def test_kernels_refuse_what_they_cannot_do(ops):
-    q = torch.zeros(1, 2, 272, device=DEV)
-    kp = torch.zeros(1, 1, 64, 272, device=DEV)
+    q = torch.zeros(1, 2, 416, device=DEV)
+    kp = torch.zeros(1, 1, 64, 416, device=DEV)
     table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
-    with pytest.raises(ops.KernelError, match="head_dim 272"):
-        ops.attn_decode(q, kp, kp, table, 1, z, z, torch.zeros(1, 544, device=DEV), torch.zeros(4096, device=DEV),
+    with pytest.raises(ops.KernelError, match="head_dim 416"):
+        ops.attn_decode(q, kp, kp, table, 1, z, z, torch.zeros(1, 832, device=DEV), torch.zeros(4096, device=DEV),
                         n_splits=1, scale=1.0, window=0)
     with pytest.raises(ops.KernelError, match="not on the GPU"):
         ops.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32, device=DEV))

@@ -511,6 +511,33 @@ def test_configurations_drawn_at_random(llogos, tmp_path, seed):
     eng.cache.audit()
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("kv_rank,rot_dim", [(272, 16), (320, 64)])
+def test_latents_longer_than_the_tensor_core_kernels_take(llogos, tmp_path, dtype, kv_rank, rot_dim):
+    """A cached row of kv_rank + rot_dim elements beyond 256: both attention mixers on the large form of the CUDA-core
+    kernels, a prompt whole and the same prompt cut in two with its end decoded."""
+    ls = [RM.layer(RM.latent(3, 24, rot_dim, 40, kv_rank, 56, 45, scaling=(4.0, 32, 16.0, 1.0)), RM.dense(48)),
+          RM.layer(RM.latent2(2, 16, rot_dim, 24, kv_rank, base=700.0), None)]
+    cfg = RM.config(ls, vocab=90, width=80, groups=5, cap=12.0)
+    d = str(tmp_path / "m")
+    w = {k: v.float() for k, v in RM.write_model(llogos, d, cfg, seed=kv_rank).items()}
+    model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 8)
+    g = torch.Generator().manual_seed(kv_rank)
+    toks = torch.randint(0, cfg["vocab"], (150,), generator=g).tolist()
+    ref = RP.forward(w, cfg, toks)
+    slot = eng.open()
+    close(eng.step([(slot, toks)], [list(range(150))]), ref, dtype, ("long latent", "whole"))
+    eng.close(slot)
+    slot = eng.open()
+    eng.step([(slot, toks[:70])], [[]])
+    close(eng.step([(slot, toks[70:140])], [list(range(70))]), ref[70:140], dtype, ("long latent", "second portion"))
+    got = [eng.step([(slot, [toks[p]])]).clone() for p in range(140, 150)]
+    close(torch.cat(got), ref[140:], dtype, ("long latent", "decoded"))
+    eng.close(slot)
+    eng.cache.audit()
+
+
 # ---- faults that random weights would hide ---------------------------------------------------------
 
 A_TOK, B_TOK = 11, 12
