@@ -21,7 +21,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import KvNeed, StateNeed
+from ..parts.base import KvNeed, MultiNeed, StateNeed
 from .slots import CacheError, FreeList, SlotTable
 
 PAGE = 64
@@ -51,6 +51,39 @@ class StateView:
     state: torch.Tensor              # [n_slots, *shape]
     unit: int
     owner: bool = True
+
+
+@dataclass
+class MultiView:
+    """What a part that declared a ``MultiNeed`` sees: ``view[name]`` is the view of the need of that name."""
+
+    views: Dict[str, object]
+    unit: object
+    owner: bool = True
+
+    def __getitem__(self, name: str):
+        return self.views[name]
+
+
+def _leaves(unit, need):
+    """``(key, leaf need)`` of everything a unit keeps: the unit itself for a plain need, ``(unit, "a.b")`` for the
+    parts of a ``MultiNeed``."""
+    if not isinstance(need, MultiNeed):
+        return [(unit, need)]
+    out = []
+
+    def walk(n: MultiNeed, prefix: str) -> None:
+        names = [k for k, _ in n.needs]
+        if len(set(names)) != len(names):
+            raise ValueError(f"cache unit {unit}: a need is named twice ({names})")
+        for name, sub in n.needs:
+            if isinstance(sub, MultiNeed):
+                walk(sub, prefix + name + ".")
+            elif sub is not None:
+                out.append(((unit, prefix + name), sub))
+
+    walk(need, "")
+    return out
 
 
 class KvGroup:
@@ -155,7 +188,9 @@ class SequenceCache:
         self.state: Dict[int, torch.Tensor] = {}
         self._longest: Dict[int, int] = {}       # slots that were truncated: the most tokens they ever held
         by_need: Dict[KvNeed, List[int]] = {}
-        for unit, need in unit_needs.items():
+        self._multi: Dict[object, MultiNeed] = {u: n for u, n in unit_needs.items() if isinstance(n, MultiNeed)}
+        flat = [leaf for u, n in unit_needs.items() if n is not None for leaf in _leaves(u, n)]
+        for unit, need in flat:
             if need is None:
                 continue
             if isinstance(need, KvNeed):
@@ -248,7 +283,10 @@ class SequenceCache:
             self.slots.length[slot] += add
 
     # ---- views -------------------------------------------------------------------------
-    def view(self, unit: int, *, owner: bool = True, keep_step_kv: bool = False, shared: Optional[Dict] = None):
+    def view(self, unit, *, owner: bool = True, keep_step_kv: bool = False, shared: Optional[Dict] = None):
+        multi = self._multi.get(unit)
+        if multi is not None:
+            return self._multi_view(unit, multi, "", owner, keep_step_kv, shared if shared is not None else {})
         g = self._group_of_unit.get(unit)
         if g is not None:
             return KvView(g.k[unit], g.v[unit], g.page_table, g.ring_pages, g.window, unit, owner,
@@ -256,6 +294,16 @@ class SequenceCache:
         if unit in self.state:
             return StateView(self.state[unit], unit, owner)
         return None
+
+    def _multi_view(self, unit, need: MultiNeed, prefix: str, owner: bool, keep_step_kv: bool, shared: Dict) -> MultiView:
+        views: Dict[str, object] = {}
+        for name, sub in need.needs:
+            if isinstance(sub, MultiNeed):
+                views[name] = self._multi_view(unit, sub, prefix + name + ".", owner, keep_step_kv, shared)
+            elif sub is not None:
+                views[name] = self.view((unit, prefix + name), owner=owner, keep_step_kv=keep_step_kv,
+                                        shared=shared.setdefault(prefix + name, {}))
+        return MultiView(views, unit, owner)
 
     def free_pages(self) -> int:
         """Pages that new sequences can still get: the scarcest group decides, among those whose pool can run

@@ -143,3 +143,7 @@ register_architecture(_fipavik.NAME, _fipavik.FipavikConfig.from_dict, _fipavik.
 from . import rukedra as _rukedra  # noqa: E402
 
 register_architecture(_rukedra.NAME, _rukedra.RukedraConfig.from_dict, _rukedra.rukedra_spec)
+
+from . import piratar as _piratar  # noqa: E402
+
+register_architecture(_piratar.NAME, _piratar.PiratarConfig.from_dict, _piratar.piratar_spec)

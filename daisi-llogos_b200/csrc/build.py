@@ -41,6 +41,7 @@ SOURCES: Dict[str, List[str]] = {
     "latent": ["latent.cu", "common.cuh", "kernel_args.h"],
     "groupnorm": ["groupnorm.cu", "common.cuh", "kernel_args.h"],
     "recurrent": ["recurrent.cu", "common.cuh", "kernel_args.h"],
+    "addnorm": ["addnorm.cu", "common.cuh", "kernel_args.h"],
     "moe": ["moe.cu", "common.cuh", "kernel_args.h"],
 }
 

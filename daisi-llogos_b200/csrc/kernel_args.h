@@ -284,6 +284,7 @@ struct MinGruArgs {
 //   score 1: s = sigmoid(logit); with groups > 0 the experts form that many equal groups of neighbours, a group's
 //            score is the sum of its group_top largest s, and only experts of the keep_groups best groups are eligible;
 //            the `top` eligible experts of largest s, weights = s / (sum of the chosen s + sum_eps) * scale.
+//   score 2: s = softmax over all experts' logits; the `top` experts of largest s, weights as for score 1.
 struct RouterRule {
   int score;
   int groups, keep_groups, group_top;
@@ -361,4 +362,151 @@ struct GroupedLinearArgs {
   long long x_group_stride, y_group_stride;   // elements by which group e's rows are shifted in x and y
   int n_rows;                                 // without token_of_row: rows from n_rows on are neither read nor written (0: all are)
   long long w_group_stride;                   // elements between the groups' matrices in w and w2 (0: n_out * n_in)
+};
+
+// Residual add of several terms, each optionally RMS-normed first, fused with the norm of the sum (addnorm.cu).  For
+// output row j (token r = rows[j] or j): for every term t, y = sum of its partials [n_partials][n_tokens][hidden]; with
+// norm_w, y = y / sqrt(mean(y^2) + norm_eps) * norm_w; residual[r] += scale * y.  Then every output o receives
+// residual[r] / sqrt(mean(residual[r]^2) + eps) * (offset + weight), or, without a weight, the row as it is (a cast).
+// Weights are float32.  No terms: the row is only normed.
+#define LLG_ADDNORM_TERMS 4
+#define LLG_ADDNORM_OUTS 2
+struct AddNormTerm {
+  const float* data;          // [n_partials][n_tokens][hidden]
+  int n_partials;
+  const float* norm_w;        // [hidden] or null
+  float norm_eps;
+  float scale;
+};
+struct AddNormOut {
+  void* out;                  // [n_out][hidden]
+  const float* weight;        // [hidden], or null: the unnormed row
+  float offset;               // added to the weight (1: a weight that holds its difference from one)
+};
+struct AddNormArgs {
+  float* residual;            // [n_tokens][hidden]
+  long long partial_stride;   // n_tokens * hidden
+  AddNormTerm terms[LLG_ADDNORM_TERMS];
+  int n_terms;
+  AddNormOut outs[LLG_ADDNORM_OUTS];
+  int n_outs;
+  int out_dtype;
+  float eps;
+  const int* rows;            // [n_out] or null
+  int n_out, hidden;
+};
+
+// Token embedding times a scale, plus a row of a second table chosen by a hash of the token and the one before it in its
+// sequence, then an RMS norm of the sum (addnorm.cu).  Row of the pair table: (prev * mul_prev + token * mul_cur) mod
+// buckets; a sequence's first token (position 0) takes row `buckets`.  The token before a step's first token comes from
+// last_token[slot], which receives the step's last token of the sequence.  norm_w null: no norm.
+struct HashEmbedArgs {
+  const void* table;          // [vocab][hidden]
+  int table_dtype;
+  float scale;
+  const void* pair_table;     // [buckets + 1][hidden] or null
+  int pair_dtype;
+  int buckets, mul_prev, mul_cur;
+  const int* token_ids;       // [n_tokens]
+  const int* positions;       // [n_tokens]
+  const int* seq_of_token;    // [n_tokens]
+  const int* cu_tokens;       // [n_seqs + 1]
+  const int* slots;           // [n_seqs]
+  int* last_token;            // [slots]
+  const float* norm_w;        // [hidden] or null
+  float norm_offset, eps;
+  float* out;                 // [n_tokens][hidden]
+  int n_tokens, vocab, hidden;
+};
+
+// out[n][j] = act(sum of the partials rows[.][n][j]) * table[token_ids[n]][col0 + j] (addnorm.cu): a gate from the
+// residual times a per-token vector looked up by the token's id.
+struct TableGateArgs {
+  const float* rows;          // [n_partials][n_tokens][width]
+  int n_partials;
+  long long partial_stride;
+  const void* table;          // [vocab][table_width]
+  int table_dtype, table_width, col0;
+  const int* token_ids;
+  int act;                    // an activation kind of llg_act
+  void* out;                  // [n_tokens][width]
+  int out_dtype;
+  int n_tokens, width, vocab;
+};
+
+// A short causal convolution per channel along every sequence of a step (recurrent.cu).  The inputs are `channels`
+// columns from col0 of a product's float32 partial sums (plus in_bias); out[n][c] = sum_j weight[c][j] *
+// input(position - taps + 1 + j) + bias[c], zeros before a sequence's start.  state[slot] holds the last taps - 1 inputs
+// of the sequence before the step and receives those after it.
+#define LLG_CONV_MAX_TAPS 16
+struct ConvArgs {
+  const float* rows;          // [n_partials][n_tokens][row_width]
+  int n_partials;
+  long long partial_stride;
+  int row_width, col0, channels, taps;
+  const float* in_bias;       // [channels] or null
+  const float* weight;        // [channels][taps]
+  const float* bias;          // [channels] or null
+  float* state;               // [slots][taps - 1][channels]
+  const int* slots;           // [n_seqs]
+  const int* cu_tokens;       // [n_seqs + 1]
+  const int* seq_of_token;    // [n_tokens]
+  const int* len_before;      // [n_seqs]
+  float* out;                 // [n_tokens][channels]
+  void* out2;                 // or null: the same values once more in out2_dtype
+  int out2_dtype;
+  int n_seqs, n_tokens;
+};
+
+// The real-gated linear recurrent unit over a step's sequences (recurrent.cu).  Per channel c of block b = c / block_width:
+// r = sigmoid(gates[n][b][o] + gate_bias[b][o]), i = sigmoid(gates[n][b][block_width + o] + gate_bias[b][block_width + o])
+// (o = c % block_width), a = exp(-decay_scale * r * softplus(lam[c])), S_t = a S_{t-1} + sqrt(1 - a^2) * i * u[n][c];
+// out[n][c] = S_t * gelu_tanh(y) with y the sum of the partials' column y_col + c plus y_bias[c].  State, carry and
+// pieces as in MinGruArgs.
+struct RgLruArgs {
+  const float* rows;          // [n_partials][n_tokens][row_width]
+  int n_partials;
+  long long partial_stride;
+  int row_width, y_col;
+  const float* y_bias;        // [size] or null
+  const float* u;             // [n_tokens][size]
+  const float* gates;         // [n_tokens][size / block_width][2 * block_width]
+  const float* gate_bias;     // [size / block_width][2 * block_width]
+  const float* lam;           // [size]
+  float decay_scale;
+  float* state;               // [slots][size]
+  const int* slots;
+  const int* cu_tokens;
+  void* out;                  // [n_tokens][size]
+  int out_dtype;
+  float* carry;
+  int pieces;
+  int n_seqs, n_tokens, size, block_width;
+};
+
+// Retention: linear attention with a fixed decay per head and no softmax (recurrent.cu).  A row of the input product holds
+// q (nh * dim) at q_col, k (nh * dim) at k_col, v (nh * vdim) at v_col and the output gate's arguments (nh * vdim) at
+// g_col.  q and k are rotated by halves over their first rotary_dim elements, k times k_scale; per head
+// S_t = decay[h] S_{t-1} + k_t v_t^T, o_t = S_t^T q_t; out[n][h] = o_t / sqrt(mean(o_t^2) + eps) * silu(g).  state[slot] is
+// [nh][dim][vdim] float32.  With carry, pieces of a sequence are run side by side from zero, joined, and run again.
+#define LLG_RETENTION_PIECE 128
+struct RetentionArgs {
+  const float* rows;          // [n_partials][n_tokens][row_width]
+  int n_partials;
+  long long partial_stride;
+  int row_width, q_col, k_col, v_col, g_col;
+  const float* cos_table;     // [table_positions][rotary_dim / 2] or null
+  const float* sin_table;
+  int rotary_dim, table_positions;
+  const int* positions;       // [n_tokens]
+  const float* decay;         // [nh]
+  float k_scale, eps;
+  float* state;               // [slots][nh][dim][vdim]
+  const int* slots;
+  const int* cu_tokens;
+  void* out;                  // [n_tokens][nh * vdim]
+  int out_dtype;
+  float* carry;               // [n_seqs][pieces][nh][dim][vdim] or null
+  int pieces;
+  int n_seqs, n_tokens, nh, dim, vdim;
 };

@@ -306,16 +306,19 @@ LLG_API int llg_latent_prep(const LatentPrepArgs* args, int out_dtype, cudaStrea
   return llg_check_launch("latent_prep");
 }
 
-LLG_API int llg_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_t stream) {
+// y_dtype: the outputs' type; float32 outputs go with inputs of either type (the sums are float32 anyway).
+LLG_API int llg_head_linear(const HeadLinearArgs* args, int dtype, int y_dtype, cudaStream_t stream) {
   const HeadLinearArgs& a = *args;
   LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.n_in > 0 && a.n_out > 0, "head_linear: bad sizes");
   LLG_REQUIRE(a.nh <= 65535, "head_linear: too many heads");
   if (a.n_tokens == 0) return 0;
   dim3 grid((a.n_tokens + HL_TN - 1) / HL_TN, (a.n_out + HL_TO - 1) / HL_TO, a.nh);
-  if (dtype == LLG_F32) llg_launch(head_linear_kernel<float, float, float>, grid, dim3(256), 0, stream, a);
-  else if (dtype == LLG_BF16)
+  if (dtype == LLG_F32 && y_dtype == LLG_F32) llg_launch(head_linear_kernel<float, float, float>, grid, dim3(256), 0, stream, a);
+  else if (dtype == LLG_BF16 && y_dtype == LLG_BF16)
     llg_launch(head_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, a);
-  else return llg_fail("head_linear: unknown dtype %d", dtype);
+  else if (dtype == LLG_BF16 && y_dtype == LLG_F32)
+    llg_launch(head_linear_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, dim3(256), 0, stream, a);
+  else return llg_fail("head_linear: unknown types %d -> %d", dtype, y_dtype);
   return llg_check_launch("head_linear");
 }
 

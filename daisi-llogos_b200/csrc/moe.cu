@@ -26,6 +26,21 @@ namespace {
 // scores and the marks of the groups that stay).
 __device__ __forceinline__ void choose_and_weigh(float* z, float* gsc, float* chosen, int n_exp, int top, const RouterRule& rule,
                                                  int* __restrict__ choice, float* __restrict__ weight, int lane) {
+  if (rule.score == 2) {
+    // scores: the softmax over every expert's logit
+    float m = -INFINITY;
+    for (int e = lane; e < n_exp; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float total = 0.f;
+    for (int e = lane; e < n_exp; e += 32) {
+      const float ev = expf(z[e] - m);
+      z[e] = ev;
+      total += ev;
+    }
+    total = warp_sum(total);
+    for (int e = lane; e < n_exp; e += 32) z[e] = z[e] / total;
+    __syncwarp();
+  }
   if (rule.score == 1) {
     for (int e = lane; e < n_exp; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
     __syncwarp();
@@ -95,7 +110,7 @@ __device__ __forceinline__ void choose_and_weigh(float* z, float* gsc, float* ch
     }
     __syncwarp();
   }
-  if (rule.score == 1) {
+  if (rule.score != 0) {
     // the chosen scores divided by their sum
     const float sv = lane < top ? chosen[lane] : 0.f;
     const float total = warp_sum(sv);
@@ -462,7 +477,7 @@ __global__ void moe_combine_vec4_kernel(const float* __restrict__ y, const int* 
 }  // namespace
 
 static int check_rule(const char* what, const RouterRule& r, int n_exp, int top) {
-  LLG_REQUIRE(r.score == 0 || r.score == 1, "%s: score kind %d is not known", what, r.score);
+  LLG_REQUIRE(r.score >= 0 && r.score <= 2, "%s: score kind %d is not known", what, r.score);
   LLG_REQUIRE(r.groups >= 0 && (r.groups == 0 || r.score == 1), "%s: groups of experts go with sigmoid scores", what);
   if (r.groups > 0) {
     LLG_REQUIRE(n_exp % r.groups == 0 && r.keep_groups > 0 && r.keep_groups <= r.groups && r.group_top > 0,
@@ -580,7 +595,7 @@ LLG_API int llg_head_linear_mma_supported(const void* x, long long x_token_strid
 
 LLG_API int llg_head_linear_mma(const void* x, long long x_token_stride, long long x_head_stride, const void* w, void* y,
                                 long long y_token_stride, long long y_head_stride, int n_tokens, int nh, int n_in, int n_out,
-                                cudaStream_t stream) {
+                                int y_dtype, cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && nh > 0 && nh <= 65535 && n_in > 0 && n_out > 0, "head_linear: bad sizes");
   LLG_REQUIRE(llg_head_linear_mma_supported(x, x_token_stride, x_head_stride, w, n_in),
               "head_linear: the tensor-core kernel wants rows that start on 16-byte boundaries");
@@ -601,9 +616,16 @@ LLG_API int llg_head_linear_mma(const void* x, long long x_token_stride, long lo
   dim3 grid(a.rows / LLG_MOE_TILE, (n_out + MM_O - 1) / MM_O, nh);
   LLG_REQUIRE(grid.y <= 65535, "head_linear: too many outputs");
   const size_t smem = 2 * (size_t)(LLG_MOE_TILE * MM_LD + MM_O * MM_LD) * sizeof(__nv_bfloat16);
-  cudaError_t err = cudaFuncSetAttribute(grouped_linear_mma_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (err != cudaSuccess) return llg_fail("head_linear: shared memory %zu: %s", smem, cudaGetErrorString(err));
-  llg_launch(grouped_linear_mma_kernel<__nv_bfloat16, false>, grid, dim3(128), smem, stream, a);
+#define HEAD_LAUNCH(YT)                                                                                                       \
+  do {                                                                                                                        \
+    cudaError_t err = cudaFuncSetAttribute(grouped_linear_mma_kernel<YT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (err != cudaSuccess) return llg_fail("head_linear: shared memory %zu: %s", smem, cudaGetErrorString(err));             \
+    llg_launch(grouped_linear_mma_kernel<YT, false>, grid, dim3(128), smem, stream, a);                                       \
+  } while (0)
+  if (y_dtype == LLG_BF16) HEAD_LAUNCH(__nv_bfloat16);
+  else if (y_dtype == LLG_F32) HEAD_LAUNCH(float);
+  else return llg_fail("head_linear: unknown output type %d", y_dtype);
+#undef HEAD_LAUNCH
   return llg_check_launch("head_linear");
 }
 

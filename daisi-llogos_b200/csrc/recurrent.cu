@@ -141,3 +141,362 @@ LLG_API int llg_mingru_scan(const MinGruArgs* args, int max_count, cudaStream_t 
   if (a.out_dtype == LLG_BF16) return mingru_launch<__nv_bfloat16>(a, stream);
   return llg_fail("mingru_scan: unknown output type %d", a.out_dtype);
 }
+
+// ---- short causal convolutions, the real-gated linear recurrent unit, retention -----------------------------------------
+//
+//   causal_conv : a thread owns one (token, channel).  The tokens of a sequence whose taps reach back before the step
+//                 (the first taps - 1 of its step tokens) are all done by the thread of the sequence's first token, which
+//                 reads the slot's state first and writes the new state last: nobody else touches that state, so nothing
+//                 of a step can read what the same step has already replaced.
+//   rglru_scan  : the minGRU scan's three modes with the unit's own gates (RgLruArgs); pieces are joined by
+//                 mingru_join_kernel, which only walks (factor, offset) pairs.
+//   retention   : a block owns one (sequence or piece, head) with the head's state [dim][vdim] in shared memory and walks
+//                 the tokens in order: S <- decay S + k v^T, o = S^T q, then the head's unit norm and the silu gate.
+//                 Rotation of q and k happens here, in float32, from the product's float32 sums.
+
+namespace {
+
+template <typename O2>
+__global__ void __launch_bounds__(128) causal_conv_kernel(ConvArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int K = a.taps;
+  const int b = a.seq_of_token[n];
+  const int t0 = a.cu_tokens[b], count = a.cu_tokens[b + 1] - t0;
+  const int p = n - t0;
+  if (p > 0 && p < K - 1) return;                  // done by the thread of the sequence's first step token
+  const float ib = a.in_bias ? a.in_bias[c] : 0.f, ob = a.bias ? a.bias[c] : 0.f;
+  float w[LLG_CONV_MAX_TAPS];
+  for (int j = 0; j < K; ++j) w[j] = a.weight[(long long)c * K + j];
+  auto input = [&](int q) {                        // the input at step token q of this sequence
+    const float* r = a.rows + (long long)(t0 + q) * a.row_width + a.col0 + c;
+    float v = r[0];
+    for (int s = 1; s < a.n_partials; ++s) v += r[s * a.partial_stride];
+    return v + ib;
+  };
+  O2* out2 = (O2*)a.out2;
+  if (p >= K - 1) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) acc = fmaf(w[j], input(p - (K - 1) + j), acc);
+    acc += ob;
+    a.out[(long long)n * a.channels + c] = acc;
+    if (out2) out2[(long long)n * a.channels + c] = from_f32<O2>(acc);
+    return;
+  }
+  // p == 0 and K >= 2: vals[0 .. K-2] the inputs before the step, vals[K-1 + q] the step's first ones
+  float vals[2 * LLG_CONV_MAX_TAPS];
+  float* st = a.state + (long long)a.slots[b] * (K - 1) * a.channels + c;
+  const int lb = a.len_before[b];
+  for (int s = 0; s < K - 1; ++s) vals[s] = (lb - (K - 1) + s >= 0) ? st[(long long)s * a.channels] : 0.f;
+  const int m = count < K - 1 ? count : K - 1;
+  for (int q = 0; q < m; ++q) vals[K - 1 + q] = input(q);
+  for (int q = 0; q < m; ++q) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) acc = fmaf(w[j], vals[q + j], acc);
+    acc += ob;
+    a.out[(long long)(t0 + q) * a.channels + c] = acc;
+    if (out2) out2[(long long)(t0 + q) * a.channels + c] = from_f32<O2>(acc);
+  }
+  float fresh[LLG_CONV_MAX_TAPS];
+  for (int s = 0; s < K - 1; ++s) {
+    const int q = count - (K - 1) + s;             // the step token whose input becomes state entry s
+    fresh[s] = q >= 0 ? (q < m ? vals[K - 1 + q] : input(q)) : vals[s + count];
+  }
+  for (int s = 0; s < K - 1; ++s) st[(long long)s * a.channels] = fresh[s];
+}
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// MODE as in mingru_scan_kernel.
+template <typename OT, int MODE>
+__global__ void __launch_bounds__(128) rglru_scan_kernel(RgLruArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  const int piece = blockIdx.y, b = blockIdx.z;
+  if (ch >= a.size) return;
+  const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
+  int lo = t_begin, hi = t_end;
+  if (MODE != 0) {
+    lo = t_begin + piece * LLG_MINGRU_PIECE;
+    if (lo > t_end) lo = t_end;
+    hi = (piece == a.pieces - 1 || lo + LLG_MINGRU_PIECE > t_end) ? t_end : lo + LLG_MINGRU_PIECE;
+  }
+  float* cr = MODE != 0 ? a.carry + (((long long)b * a.pieces + piece) * 2) * a.size + ch : nullptr;
+  const int bw = a.block_width;
+  const int blk = ch / bw, o = ch - blk * bw;
+  const long long gcol = (long long)blk * 2 * bw + o;        // r's argument; i's lies bw further
+  const float br = a.gate_bias[gcol], bi = a.gate_bias[gcol + bw];
+  const float by = a.y_bias ? a.y_bias[ch] : 0.f;
+  const float rate = -a.decay_scale * softplus_f(a.lam[ch]);
+  float S = 0.f, A = 1.f;
+  if (MODE == 0) S = a.state[(long long)a.slots[b] * a.size + ch];
+  if (MODE == 2) {
+    if (lo >= hi) return;
+    S = cr[a.size];
+  }
+  OT* out = (OT*)a.out;
+  const long long grow = 2LL * a.size;
+  for (int n0 = lo; n0 < hi; n0 += SCAN_BATCH) {
+    float gr[SCAN_BATCH], gi[SCAN_BATCH], u[SCAN_BATCH], y[SCAN_BATCH];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (n0 + k < hi) {
+        gr[k] = a.gates[(n0 + k) * grow + gcol] + br;
+        gi[k] = a.gates[(n0 + k) * grow + gcol + bw] + bi;
+        u[k] = a.u[(long long)(n0 + k) * a.size + ch];
+        y[k] = by;
+      }
+    }
+    if (MODE != 1) {
+      for (int s = 0; s < a.n_partials; ++s) {
+        const float* p = a.rows + s * a.partial_stride + (long long)n0 * a.row_width + a.y_col + ch;
+#pragma unroll
+        for (int k = 0; k < SCAN_BATCH; ++k)
+          if (n0 + k < hi) y[k] += p[(long long)k * a.row_width];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      if (n0 + k < hi) {
+        const float r = sigmoid_f(gr[k]), i = sigmoid_f(gi[k]);
+        const float la = rate * r;
+        const float at = expf(la);
+        const float drive = sqrtf(-expm1f(2.0f * la)) * i * u[k];      // sqrt(1 - a^2) without the cancellation near a = 1
+        S = at * S + drive;
+        if (MODE == 1) A *= at;
+        else out[(long long)(n0 + k) * a.size + ch] = from_f32<OT>(S * llg_act(1, y[k]));
+      }
+    }
+  }
+  if (MODE == 0) a.state[(long long)a.slots[b] * a.size + ch] = S;
+  if (MODE == 1) {
+    cr[0] = A;
+    cr[a.size] = S;
+  }
+}
+
+template <typename OT>
+int rglru_launch(const RgLruArgs& a, cudaStream_t stream) {
+  const unsigned cb = (unsigned)((a.size + 127) / 128);
+  if (!a.carry) {
+    llg_launch(rglru_scan_kernel<OT, 0>, dim3(cb, 1, a.n_seqs), dim3(128), 0, stream, a);
+    return llg_check_launch("rglru_scan");
+  }
+  MinGruArgs j;
+  memset(&j, 0, sizeof(j));
+  j.state = a.state;
+  j.slots = a.slots;
+  j.carry = a.carry;
+  j.pieces = a.pieces;
+  j.size = a.size;
+  llg_launch(rglru_scan_kernel<OT, 1>, dim3(cb, a.pieces, a.n_seqs), dim3(128), 0, stream, a);
+  llg_launch(mingru_join_kernel, dim3(cb, a.n_seqs), dim3(128), 0, stream, j);
+  llg_launch(rglru_scan_kernel<OT, 2>, dim3(cb, a.pieces, a.n_seqs), dim3(128), 0, stream, a);
+  return llg_check_launch("rglru_scan (pieces)");
+}
+
+constexpr int RET_THREADS = 256;
+
+// Shared memory: S [dim * vdim] | q [dim] | k [dim] | v [vdim] | g [vdim] | partial o [slices * vdim].
+// MODE 0: the whole sequence from state[slot]; MODE 1: a piece from zero, its state to carry; MODE 2: a piece from carry.
+template <typename OT, int MODE>
+__global__ void __launch_bounds__(RET_THREADS) retention_kernel(RetentionArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float smem[];
+  __shared__ float part[32];
+  const int h = blockIdx.x, piece = blockIdx.y, b = blockIdx.z;
+  const int dim = a.dim, vdim = a.vdim, nst = dim * vdim;
+  const int slices = RET_THREADS / vdim > 0 ? RET_THREADS / vdim : 1;
+  const int cols = RET_THREADS / slices;
+  const int sl = threadIdx.x / cols, tj = threadIdx.x - sl * cols;
+  float* S = smem;
+  float* sq = S + nst;
+  float* sk = sq + dim;
+  float* sv = sk + dim;
+  float* sg = sv + vdim;
+  float* so = sg + vdim;
+  const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
+  int lo = t_begin, hi = t_end;
+  if (MODE != 0) {
+    lo = t_begin + piece * LLG_RETENTION_PIECE;
+    if (lo > t_end) lo = t_end;
+    hi = (piece == a.pieces - 1 || lo + LLG_RETENTION_PIECE > t_end) ? t_end : lo + LLG_RETENTION_PIECE;
+  }
+  float* gstate = a.state + ((long long)a.slots[b] * a.nh + h) * nst;
+  float* cr = MODE != 0 ? a.carry + (((long long)b * a.pieces + piece) * a.nh + h) * nst : nullptr;
+  if (MODE == 2 && lo >= hi) return;
+  for (int e = threadIdx.x; e < nst; e += RET_THREADS) S[e] = MODE == 0 ? gstate[e] : MODE == 1 ? 0.f : cr[e];
+  const float decay = a.decay[h];
+  const int rd = a.cos_table ? a.rotary_dim : 0, half = rd / 2;
+  OT* out = (OT*)a.out;
+  for (int n = lo; n < hi; ++n) {
+    const float* row = a.rows + (long long)n * a.row_width;
+    auto summed = [&](int col) {
+      float v = row[col];
+      for (int s = 1; s < a.n_partials; ++s) v += row[s * a.partial_stride + col];
+      return v;
+    };
+    int pos = a.positions[n];
+    if (pos >= a.table_positions) pos = a.table_positions - 1;
+    for (int i = threadIdx.x; i < dim; i += RET_THREADS) {
+      float kv = summed(a.k_col + h * dim + i);
+      float qv = MODE != 1 ? summed(a.q_col + h * dim + i) : 0.f;
+      if (i < rd) {
+        const int f = i < half ? i : i - half;
+        const int ip = i < half ? i + half : i - half;
+        const float c = a.cos_table[(long long)pos * half + f], s = a.sin_table[(long long)pos * half + f];
+        const float kp = summed(a.k_col + h * dim + ip);
+        kv = i < half ? kv * c - kp * s : kv * c + kp * s;
+        if (MODE != 1) {
+          const float qp = summed(a.q_col + h * dim + ip);
+          qv = i < half ? qv * c - qp * s : qv * c + qp * s;
+        }
+      }
+      sk[i] = kv * a.k_scale;
+      sq[i] = qv;
+    }
+    for (int j = threadIdx.x; j < vdim; j += RET_THREADS) {
+      sv[j] = summed(a.v_col + h * vdim + j);
+      if (MODE != 1) sg[j] = summed(a.g_col + h * vdim + j);
+    }
+    __syncthreads();
+    for (int j = tj; j < vdim; j += cols) {
+      const float vj = sv[j];
+      float o = 0.f;
+      for (int i = sl; i < dim; i += slices) {
+        const float s = fmaf(decay, S[i * vdim + j], sk[i] * vj);
+        S[i * vdim + j] = s;
+        o = fmaf(s, sq[i], o);
+      }
+      if (MODE != 1) so[sl * vdim + j] = o;
+    }
+    if (MODE != 1) {
+      __syncthreads();
+      float ss = 0.f;
+      for (int j = threadIdx.x; j < vdim; j += RET_THREADS) {
+        float o = so[j];
+        for (int s = 1; s < slices; ++s) o += so[s * vdim + j];
+        so[j] = o;
+        ss = fmaf(o, o, ss);
+      }
+      ss = block_sum(ss, part);
+      const float inv = 1.0f / sqrtf(ss / (float)vdim + a.eps);
+      for (int j = threadIdx.x; j < vdim; j += RET_THREADS) {
+        const float g = sg[j];
+        out[((long long)n * a.nh + h) * vdim + j] = from_f32<OT>(so[j] * inv * (g / (1.0f + expf(-g))));
+      }
+    }
+    __syncthreads();
+  }
+  if (MODE == 0)
+    for (int e = threadIdx.x; e < nst; e += RET_THREADS) gstate[e] = S[e];
+  if (MODE == 1)
+    for (int e = threadIdx.x; e < nst; e += RET_THREADS) cr[e] = S[e];
+}
+
+// Walks a sequence's pieces: piece p starts from what the pieces before it make of the sequence's state.
+__global__ void __launch_bounds__(256) retention_join_kernel(RetentionArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int nst = a.dim * a.vdim;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= nst) return;
+  const float decay = a.decay[h];
+  const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
+  float* st = a.state + ((long long)a.slots[b] * a.nh + h) * nst + e;
+  float S = *st;
+  for (int p = 0; p < a.pieces; ++p) {
+    int lo = t_begin + p * LLG_RETENTION_PIECE;
+    if (lo > t_end) lo = t_end;
+    const int hi = (p == a.pieces - 1 || lo + LLG_RETENTION_PIECE > t_end) ? t_end : lo + LLG_RETENTION_PIECE;
+    float* cr = a.carry + (((long long)b * a.pieces + p) * a.nh + h) * nst + e;
+    const float reached = *cr;
+    *cr = S;
+    float A = 1.f;
+    for (int t = lo; t < hi; ++t) A *= decay;
+    S = A * S + reached;
+  }
+  *st = S;
+}
+
+template <typename OT>
+int retention_launch(const RetentionArgs& a, size_t smem, cudaStream_t stream) {
+#define RET_ATTR(K)                                                                                             \
+  if (smem > 48 * 1024) {                                                                                       \
+    cudaError_t e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    if (e != cudaSuccess) return llg_fail("retention: shared memory %zu: %s", smem, cudaGetErrorString(e));     \
+  }
+  if (!a.carry) {
+    RET_ATTR((retention_kernel<OT, 0>));
+    llg_launch(retention_kernel<OT, 0>, dim3(a.nh, 1, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
+    return llg_check_launch("retention");
+  }
+  RET_ATTR((retention_kernel<OT, 1>));
+  RET_ATTR((retention_kernel<OT, 2>));
+#undef RET_ATTR
+  const int nst = a.dim * a.vdim;
+  llg_launch(retention_kernel<OT, 1>, dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
+  llg_launch(retention_join_kernel, dim3((nst + 255) / 256, a.nh, a.n_seqs), dim3(256), 0, stream, a);
+  llg_launch(retention_kernel<OT, 2>, dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
+  return llg_check_launch("retention (pieces)");
+}
+
+}  // namespace
+
+LLG_API int llg_conv_max_taps() { return LLG_CONV_MAX_TAPS; }
+LLG_API int llg_retention_piece() { return LLG_RETENTION_PIECE; }
+
+LLG_API int llg_causal_conv(const ConvArgs* args, cudaStream_t stream) {
+  const ConvArgs& a = *args;
+  LLG_REQUIRE(a.n_seqs >= 0 && a.n_tokens >= 0 && a.channels > 0 && a.n_partials >= 1, "causal_conv: bad sizes");
+  LLG_REQUIRE(a.taps >= 1 && a.taps <= LLG_CONV_MAX_TAPS, "causal_conv: %d taps (1 to %d)", a.taps, LLG_CONV_MAX_TAPS);
+  LLG_REQUIRE(a.col0 >= 0 && a.col0 + a.channels <= a.row_width, "causal_conv: %d channels at column %d of %d", a.channels, a.col0, a.row_width);
+  LLG_REQUIRE(a.taps == 1 || a.state, "causal_conv: more than one tap needs the sequences' state");
+  if (a.n_tokens == 0) return 0;
+  dim3 grid(a.n_tokens, (a.channels + 127) / 128);
+  LLG_REQUIRE(grid.y <= 65535, "causal_conv: too many channels");
+  if (!a.out2 || a.out2_dtype == LLG_F32) llg_launch(causal_conv_kernel<float>, grid, dim3(128), 0, stream, a);
+  else if (a.out2_dtype == LLG_BF16) llg_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
+  else return llg_fail("causal_conv: unknown output type %d", a.out2_dtype);
+  return llg_check_launch("causal_conv");
+}
+
+LLG_API int llg_rglru_scan(const RgLruArgs* args, int max_count, cudaStream_t stream) {
+  const RgLruArgs& a = *args;
+  LLG_REQUIRE(a.n_seqs >= 0 && a.n_tokens >= 0 && a.size > 0 && a.n_partials >= 1, "rglru_scan: bad sizes");
+  LLG_REQUIRE(a.block_width > 0 && a.size % a.block_width == 0, "rglru_scan: %d channels in blocks of %d", a.size, a.block_width);
+  LLG_REQUIRE(a.y_col >= 0 && a.y_col + a.size <= a.row_width, "rglru_scan: %d channels at column %d of %d", a.size, a.y_col, a.row_width);
+  LLG_REQUIRE(a.n_seqs <= 65535, "rglru_scan: %d sequences in a step (at most 65535)", a.n_seqs);
+  if (a.carry)
+    LLG_REQUIRE(a.pieces >= 1 && a.pieces <= 65535 && (long long)a.pieces * LLG_MINGRU_PIECE >= max_count,
+                "rglru_scan: %d pieces of %d tokens do not hold a sequence of %d", a.pieces, LLG_MINGRU_PIECE, max_count);
+  if (a.n_seqs == 0 || a.n_tokens == 0) return 0;
+  if (a.out_dtype == LLG_F32) return rglru_launch<float>(a, stream);
+  if (a.out_dtype == LLG_BF16) return rglru_launch<__nv_bfloat16>(a, stream);
+  return llg_fail("rglru_scan: unknown output type %d", a.out_dtype);
+}
+
+LLG_API int llg_retention(const RetentionArgs* args, int max_count, cudaStream_t stream) {
+  const RetentionArgs& a = *args;
+  LLG_REQUIRE(a.n_seqs >= 0 && a.n_tokens >= 0 && a.nh > 0 && a.dim > 0 && a.vdim > 0 && a.n_partials >= 1, "retention: bad sizes");
+  LLG_REQUIRE(a.n_seqs <= 65535 && a.nh <= 65535, "retention: too many sequences or heads");
+  LLG_REQUIRE(!a.cos_table || (a.rotary_dim > 0 && a.rotary_dim % 2 == 0 && a.rotary_dim <= a.dim && a.table_positions > 0),
+              "retention: %d rotated elements of a head of %d", a.rotary_dim, a.dim);
+  LLG_REQUIRE(a.eps > 0.f, "retention: eps %g", a.eps);
+  if (a.carry)
+    LLG_REQUIRE(a.pieces >= 1 && a.pieces <= 65535 && (long long)a.pieces * LLG_RETENTION_PIECE >= max_count,
+                "retention: %d pieces of %d tokens do not hold a sequence of %d", a.pieces, LLG_RETENTION_PIECE, max_count);
+  const int slices = RET_THREADS / a.vdim > 0 ? RET_THREADS / a.vdim : 1;
+  const size_t smem = ((size_t)a.dim * a.vdim + 2 * (size_t)a.dim + 2 * (size_t)a.vdim + (size_t)slices * a.vdim) * sizeof(float);
+  LLG_REQUIRE(smem <= 220 * 1024, "retention: a head's state of %d x %d does not fit shared memory", a.dim, a.vdim);
+  if (a.n_seqs == 0 || a.n_tokens == 0) return 0;
+  if (a.out_dtype == LLG_F32) return retention_launch<float>(a, smem, stream);
+  if (a.out_dtype == LLG_BF16) return retention_launch<__nv_bfloat16>(a, smem, stream);
+  return llg_fail("retention: unknown output type %d", a.out_dtype);
+}

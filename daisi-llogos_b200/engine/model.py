@@ -29,6 +29,9 @@ from ..parts import recurrent as _recurrent  # noqa: F401
 from ..parts import sandwich as _sandwich  # noqa: F401
 
 
+EMBEDDING_UNIT = "embedding"      # the cache unit of an embedding that keeps state (schedule entries are numbered)
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, *, dtype: torch.dtype, device: torch.device, ops):
         spec.validate()
@@ -116,6 +119,8 @@ class DecoderModel:
     def cache_needs(self) -> Dict[int, object]:
         """Schedule entry -> what its mixer keeps (entries that borrow a cache keep nothing)."""
         needs = {}
+        if self.embedding.cache_need() is not None:
+            needs[EMBEDDING_UNIT] = self.embedding.cache_need()
         for e_i, e in enumerate(self.spec.schedule):
             if e.cache_of is not None:
                 continue
@@ -128,7 +133,11 @@ class DecoderModel:
     def forward(self, ctx, cache, rows: Optional[torch.Tensor], runner=None) -> torch.Tensor:
         """Runs the step's tokens; returns float32 logits of ``rows`` (token indices), [len(rows), vocab].
         ``runner``: an ``engine.runner.BlockRunner`` built for this model and cache; it then runs the layers."""
-        residual = self.embedding.forward(ctx)
+        if self.embedding.cache_need() is not None:
+            # an embedding that keeps something per sequence (the token before) has a cache unit of its own
+            residual = self.embedding.forward(ctx, cache.view(EMBEDDING_UNIT))
+        else:
+            residual = self.embedding.forward(ctx)
         for enc in self.encodings.values():
             enc.on_embeddings(residual, ctx)
         pending: Optional[Branch] = None

@@ -212,6 +212,76 @@ class _MinGruArgs(Structure):
     ]
 
 
+class _AddNormTerm(Structure):
+    _fields_ = [("data", c_void_p), ("n_partials", c_int), ("norm_w", c_void_p), ("norm_eps", c_float), ("scale", c_float)]
+
+
+class _AddNormOut(Structure):
+    _fields_ = [("out", c_void_p), ("weight", c_void_p), ("offset", c_float)]
+
+
+ADDNORM_MAX_TERMS = 4        # terms and outputs of ``multi_add_rmsnorm``; checked against the library at first use
+ADDNORM_MAX_OUTS = 2
+
+
+class _AddNormArgs(Structure):
+    _fields_ = [
+        ("residual", c_void_p), ("partial_stride", c_longlong), ("terms", _AddNormTerm * ADDNORM_MAX_TERMS), ("n_terms", c_int),
+        ("outs", _AddNormOut * ADDNORM_MAX_OUTS), ("n_outs", c_int), ("out_dtype", c_int), ("eps", c_float),
+        ("rows", c_void_p), ("n_out", c_int), ("hidden", c_int),
+    ]
+
+
+class _HashEmbedArgs(Structure):
+    _fields_ = [
+        ("table", c_void_p), ("table_dtype", c_int), ("scale", c_float), ("pair_table", c_void_p), ("pair_dtype", c_int),
+        ("buckets", c_int), ("mul_prev", c_int), ("mul_cur", c_int),
+        ("token_ids", c_void_p), ("positions", c_void_p), ("seq_of_token", c_void_p), ("cu_tokens", c_void_p),
+        ("slots", c_void_p), ("last_token", c_void_p), ("norm_w", c_void_p), ("norm_offset", c_float), ("eps", c_float),
+        ("out", c_void_p), ("n_tokens", c_int), ("vocab", c_int), ("hidden", c_int),
+    ]
+
+
+class _TableGateArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong), ("table", c_void_p),
+        ("table_dtype", c_int), ("table_width", c_int), ("col0", c_int), ("token_ids", c_void_p), ("act", c_int),
+        ("out", c_void_p), ("out_dtype", c_int), ("n_tokens", c_int), ("width", c_int), ("vocab", c_int),
+    ]
+
+
+class _ConvArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("row_width", c_int), ("col0", c_int), ("channels", c_int), ("taps", c_int),
+        ("in_bias", c_void_p), ("weight", c_void_p), ("bias", c_void_p), ("state", c_void_p),
+        ("slots", c_void_p), ("cu_tokens", c_void_p), ("seq_of_token", c_void_p), ("len_before", c_void_p),
+        ("out", c_void_p), ("out2", c_void_p), ("out2_dtype", c_int), ("n_seqs", c_int), ("n_tokens", c_int),
+    ]
+
+
+class _RgLruArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong), ("row_width", c_int), ("y_col", c_int),
+        ("y_bias", c_void_p), ("u", c_void_p), ("gates", c_void_p), ("gate_bias", c_void_p), ("lam", c_void_p),
+        ("decay_scale", c_float), ("state", c_void_p), ("slots", c_void_p), ("cu_tokens", c_void_p),
+        ("out", c_void_p), ("out_dtype", c_int), ("carry", c_void_p), ("pieces", c_int),
+        ("n_seqs", c_int), ("n_tokens", c_int), ("size", c_int), ("block_width", c_int),
+    ]
+
+
+class _RetentionArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("row_width", c_int), ("q_col", c_int), ("k_col", c_int), ("v_col", c_int), ("g_col", c_int),
+        ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int), ("table_positions", c_int),
+        ("positions", c_void_p), ("decay", c_void_p), ("k_scale", c_float), ("eps", c_float),
+        ("state", c_void_p), ("slots", c_void_p), ("cu_tokens", c_void_p), ("out", c_void_p), ("out_dtype", c_int),
+        ("carry", c_void_p), ("pieces", c_int),
+        ("n_seqs", c_int), ("n_tokens", c_int), ("nh", c_int), ("dim", c_int), ("vdim", c_int),
+    ]
+
+
 class _RouterRule(Structure):
     _fields_ = [("score", c_int), ("groups", c_int), ("keep_groups", c_int), ("group_top", c_int), ("scale", c_float),
                 ("sum_eps", c_float)]
@@ -344,7 +414,18 @@ def _load_lib(name: str):
         lib.llg_norm_max_groups.restype = c_int
         if lib.llg_norm_max_groups() != NORM_MAX_GROUPS:
             raise KernelError(f"the norm kernel takes {lib.llg_norm_max_groups()} groups, Python expects {NORM_MAX_GROUPS}")
+    elif name == "addnorm":
+        lib.llg_multi_add_rmsnorm.argtypes = [POINTER(_AddNormArgs), c_void_p]
+        lib.llg_hash_embed.argtypes = [POINTER(_HashEmbedArgs), c_void_p]
+        lib.llg_table_gate.argtypes = [POINTER(_TableGateArgs), c_void_p]
+        if (lib.llg_addnorm_max_terms(), lib.llg_addnorm_max_outs()) != (ADDNORM_MAX_TERMS, ADDNORM_MAX_OUTS):
+            raise KernelError("the add-and-norm kernel's limits differ from what Python expects")
     elif name == "recurrent":
+        lib.llg_causal_conv.argtypes = [POINTER(_ConvArgs), c_void_p]
+        lib.llg_rglru_scan.argtypes = [POINTER(_RgLruArgs), c_int, c_void_p]
+        lib.llg_retention.argtypes = [POINTER(_RetentionArgs), c_int, c_void_p]
+        if (lib.llg_conv_max_taps(), lib.llg_retention_piece()) != (CONV_MAX_TAPS, RETENTION_PIECE):
+            raise KernelError("the convolution's taps or retention's pieces differ from what Python expects")
         lib.llg_mingru_scan.argtypes = [POINTER(_MinGruArgs), c_int, c_void_p]
         lib.llg_mingru_piece.restype = c_int
         if lib.llg_mingru_piece() != MINGRU_PIECE:
@@ -353,13 +434,13 @@ def _load_lib(name: str):
         lib.llg_latent_prep.argtypes = [POINTER(_LatentPrepArgs), c_int, c_void_p]
         lib.llg_sigmoid_gate.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int,
                                          c_void_p]
-        lib.llg_head_linear.argtypes = [POINTER(_HeadLinearArgs), c_int, c_void_p]
+        lib.llg_head_linear.argtypes = [POINTER(_HeadLinearArgs), c_int, c_int, c_void_p]
     elif name == "moe":
         lib.llg_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                       POINTER(_RouterRule), c_void_p, c_void_p]
         lib.llg_head_linear_mma_supported.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_int]
         lib.llg_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
-                                            c_int, c_int, c_int, c_int, c_void_p]
+                                            c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.llg_moe_topk.argtypes = [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                      POINTER(_RouterRule), c_void_p, c_void_p]
         lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
@@ -896,9 +977,188 @@ def mingru_scan(rows: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, slo
     _check(lib, lib.llg_mingru_scan(byref(a), max_count, _stream()), kernels=3 if carry is not None else 1)
 
 
+def multi_add_rmsnorm(residual: torch.Tensor, terms, outs, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """The residual add of several terms fused with the norm of the sum.  ``terms``: a sequence of ``(data, norm_weight, norm_eps,
+    scale)`` with ``data`` float32 partials ``[S, N, H]``; a term with a ``norm_weight`` (float32 ``[H]``) is divided by its
+    own root mean square and multiplied by that weight before ``scale`` times it is added to ``residual`` (float32
+    ``[N, H]``).  ``outs``: a sequence of ``(out, weight, offset)``: ``out[j] = residual[r] / sqrt(mean(residual[r]^2) + eps) *
+    (offset + weight)`` for r = ``rows[j]`` or j, or, with ``weight`` None, the row as it is in ``out``'s type.  All outputs
+    share one dtype."""
+    lib = _lib("addnorm")
+    n, hidden = residual.shape
+    if len(terms) > ADDNORM_MAX_TERMS or not 1 <= len(outs) <= ADDNORM_MAX_OUTS:
+        raise KernelError(f"multi_add_rmsnorm: {len(terms)} terms (at most {ADDNORM_MAX_TERMS}) and {len(outs)} outputs "
+                          f"(1 to {ADDNORM_MAX_OUTS})")
+    a = _AddNormArgs()
+    a.residual, a.partial_stride = _ptr(residual, torch.float32), n * hidden
+    for i, (data, w, w_eps, scale) in enumerate(terms):
+        assert data.dim() == 3 and data.shape[1:] == (n, hidden), (data.shape, residual.shape)
+        assert w is None or w.shape == (hidden,)
+        a.terms[i] = _AddNormTerm(_ptr(data, torch.float32), data.shape[0], _ptr(w, torch.float32), float(w_eps), float(scale))
+    a.n_terms = len(terms)
+    m = outs[0][0].shape[0]
+    assert (rows.numel() == m) if rows is not None else (m == n)
+    for i, (out, w, offset) in enumerate(outs):
+        assert out.shape == (m, hidden) and (w is None or w.shape == (hidden,))
+        if out.dtype != outs[0][0].dtype:
+            raise KernelError("multi_add_rmsnorm: all outputs must share one dtype")
+        a.outs[i] = _AddNormOut(_ptr(out), _ptr(w, torch.float32), float(offset))
+    a.n_outs, a.out_dtype, a.eps = len(outs), _dt(outs[0][0]), float(eps)
+    a.rows, a.n_out, a.hidden = _ptr(rows, torch.int32), m, hidden
+    _check(lib, lib.llg_multi_add_rmsnorm(byref(a), _stream()))
+
+
+def hash_embed(table: torch.Tensor, scale: float, pair_table: Optional[torch.Tensor], buckets: int, mul_prev: int, mul_cur: int,
+               token_ids: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, cu_tokens: torch.Tensor,
+               slots: torch.Tensor, last_token: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], norm_offset: float,
+               eps: float, out_residual: torch.Tensor) -> None:
+    """out_residual[n] = norm(scale * table[token] + pair_table[(prev * mul_prev + token * mul_cur) mod buckets]) in
+    float32, where ``prev`` is the token before in the same sequence and a sequence's first token takes the pair table's
+    row ``buckets``.  ``last_token`` (int32 ``[slots, 1]``) gives the token before a step's first one and receives the
+    step's last.  ``norm_w`` (float32, or None for no norm): ``x / sqrt(mean(x^2) + eps) * (norm_offset + norm_w)``."""
+    lib = _lib("addnorm")
+    vocab, hidden = table.shape
+    n = token_ids.numel()
+    assert out_residual.shape == (n, hidden)
+    a = _HashEmbedArgs()
+    a.table, a.table_dtype, a.scale = _ptr(table), _dt(table), float(scale)
+    if pair_table is not None:
+        assert pair_table.shape == (buckets + 1, hidden) and last_token is not None
+        a.pair_table, a.pair_dtype = _ptr(pair_table), _dt(pair_table)
+        a.buckets, a.mul_prev, a.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        a.last_token = _ptr(last_token, torch.int32)
+    a.token_ids, a.positions = _ptr(token_ids, torch.int32), _ptr(positions, torch.int32)
+    a.seq_of_token, a.cu_tokens = _ptr(seq_of_token, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.slots = _ptr(slots, torch.int32)
+    a.norm_w, a.norm_offset, a.eps = _ptr(norm_w, torch.float32), float(norm_offset), float(eps)
+    a.out, a.n_tokens, a.vocab, a.hidden = _ptr(out_residual, torch.float32), n, vocab, hidden
+    _check(lib, lib.llg_hash_embed(byref(a), _stream()))
+
+
+def table_gate(rows: torch.Tensor, table: torch.Tensor, col0: int, token_ids: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out[n, j] = act(sum of the partials ``rows[:, n, j]``) * table[token_ids[n], col0 + j]; ``kind`` one of
+    ``ACTIVATIONS``."""
+    lib = _lib("addnorm")
+    p_n, n, width = rows.shape
+    assert out.shape == (n, width) and table.dim() == 2 and token_ids.numel() == n
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"table_gate: activation '{kind}' is not known ({', '.join(ACTIVATIONS)})")
+    a = _TableGateArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.table, a.table_dtype, a.table_width, a.col0 = _ptr(table), _dt(table), table.shape[1], int(col0)
+    a.token_ids, a.act = _ptr(token_ids, torch.int32), ACTIVATIONS[kind]
+    a.out, a.out_dtype, a.n_tokens, a.width, a.vocab = _ptr(out), _dt(out), n, width, table.shape[0]
+    _check(lib, lib.llg_table_gate(byref(a), _stream()))
+
+
+CONV_MAX_TAPS = 16           # taps of a short convolution; checked against the library at first use
+RETENTION_PIECE = 128        # tokens of a piece of retention's walk; checked against the library at first use
+
+
+def causal_conv(rows: torch.Tensor, col0: int, weight: torch.Tensor, state: Optional[torch.Tensor], slots: torch.Tensor,
+                cu_tokens: torch.Tensor, seq_of_token: torch.Tensor, len_before: torch.Tensor, out: torch.Tensor,
+                in_bias: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                out2: Optional[torch.Tensor] = None) -> None:
+    """A causal convolution per channel along every sequence of a step.  The inputs are the ``C`` columns from ``col0`` of
+    float32 partials ``rows`` ``[P, N, width]``, plus ``in_bias``; ``out[n, c] = sum_j weight[c, j] * input(position - K + 1 + j)
+    + bias[c]`` (``weight`` float32 ``[C, K]``; zeros before a sequence's start).  ``state`` float32 ``[slots, K - 1, C]`` holds a
+    sequence's last ``K - 1`` inputs before the step and receives those after it.  ``out`` float32 ``[N, C]``; ``out2``: the
+    same once more in another type."""
+    lib = _lib("recurrent")
+    p_n, n, width = rows.shape
+    c, k = weight.shape
+    assert out.shape == (n, c) and (out2 is None or out2.shape == (n, c))
+    assert k == 1 or (state is not None and state.shape[1:] == (k - 1, c)), "the state holds taps - 1 rows of inputs"
+    a = _ConvArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.row_width, a.col0, a.channels, a.taps = width, int(col0), c, k
+    a.in_bias, a.weight, a.bias = _ptr(in_bias, torch.float32), _ptr(weight, torch.float32), _ptr(bias, torch.float32)
+    a.state = _ptr(state, torch.float32) if k > 1 else None
+    a.slots, a.cu_tokens = _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.seq_of_token, a.len_before = _ptr(seq_of_token, torch.int32), _ptr(len_before, torch.int32)
+    a.out, a.out2 = _ptr(out, torch.float32), _ptr(out2)
+    a.out2_dtype = _dt(out2) if out2 is not None else F32
+    a.n_seqs, a.n_tokens = slots.numel(), n
+    _check(lib, lib.llg_causal_conv(byref(a), _stream()))
+
+
+def rglru_scan(rows: torch.Tensor, y_col: int, y_bias: Optional[torch.Tensor], u: torch.Tensor, gates: torch.Tensor,
+               gate_bias: torch.Tensor, lam: torch.Tensor, decay_scale: float, state: torch.Tensor, slots: torch.Tensor,
+               cu_tokens: torch.Tensor, out: torch.Tensor, carry: Optional[torch.Tensor] = None) -> None:
+    """The real-gated linear recurrent unit along every sequence of a step.  Per channel c in block b (of ``bw`` channels,
+    o = c mod bw): ``r = sigmoid(gates[n, b, o] + gate_bias[b, o])``, ``i = sigmoid(gates[n, b, bw + o] + gate_bias[b, bw + o])``,
+    ``a = exp(-decay_scale r softplus(lam[c]))``, ``S_t = a S_{t-1} + sqrt(1 - a^2) i u[n, c]``; ``out[n, c] = S_t gelu_tanh(y)``
+    with y the sum of the partials ``rows[:, n, y_col + c]`` plus ``y_bias[c]``.  ``gates`` float32 ``[N, blocks, 2 bw]``, ``u``
+    float32 ``[N, size]``, ``state`` float32 ``[slots, size]``; ``carry`` as in ``mingru_scan``."""
+    lib = _lib("recurrent")
+    p_n, n, width = rows.shape
+    size = out.shape[1]
+    blocks, two_bw = gates.shape[1], gates.shape[2]
+    n_seqs = slots.numel()
+    assert out.shape == (n, size) and u.shape == (n, size) and gates.shape[0] == n and blocks * two_bw == 2 * size
+    assert gate_bias.shape == (blocks, two_bw) and lam.shape == (size,) and state.shape[1:] == (size,)
+    a = _RgLruArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.row_width, a.y_col, a.y_bias = width, int(y_col), _ptr(y_bias, torch.float32)
+    a.u, a.gates, a.gate_bias = _ptr(u, torch.float32), _ptr(gates, torch.float32), _ptr(gate_bias, torch.float32)
+    a.lam, a.decay_scale = _ptr(lam, torch.float32), float(decay_scale)
+    a.state, a.slots, a.cu_tokens = _ptr(state, torch.float32), _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.out, a.out_dtype = _ptr(out), _dt(out)
+    max_count = 0
+    if carry is not None:
+        assert carry.dim() == 4 and carry.shape[0] >= n_seqs and carry.shape[2:] == (2, size) and carry.is_contiguous()
+        a.carry, a.pieces = _ptr(carry, torch.float32), carry.shape[1]
+        max_count = min(n, carry.shape[1] * MINGRU_PIECE)
+    a.n_seqs, a.n_tokens, a.size, a.block_width = n_seqs, n, size, two_bw // 2
+    _check(lib, lib.llg_rglru_scan(byref(a), max_count, _stream()), kernels=3 if carry is not None else 1)
+
+
+def retention_pieces(max_count: int) -> int:
+    """Pieces per sequence that ``retention`` wants a carry for when the longest sequence of a step brings ``max_count``
+    tokens (1: no carry)."""
+    return max(1, -(-int(max_count) // RETENTION_PIECE))
+
+
+def retention(rows: torch.Tensor, *, q_col: int, k_col: int, v_col: int, g_col: int, n_heads: int, dim: int, vdim: int,
+              cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+              decay: torch.Tensor, k_scale: float, eps: float, state: torch.Tensor, slots: torch.Tensor,
+              cu_tokens: torch.Tensor, out: torch.Tensor, carry: Optional[torch.Tensor] = None) -> None:
+    """Retention along every sequence of a step, from float32 partials ``rows`` ``[P, N, width]`` that hold q, k (``n_heads *
+    dim`` columns each), v and the gate's arguments (``n_heads * vdim`` each) at their columns.  q and k are rotated by
+    halves over their first ``rotary_dim`` elements, k times ``k_scale``; per head ``S_t = decay[h] S_{t-1} + k_t v_t^T``,
+    ``o_t = S_t^T q_t``, ``out[n, h] = o_t / sqrt(mean(o_t^2) + eps) * silu(g)``.  ``state`` float32 ``[slots, n_heads, dim, vdim]``;
+    ``carry`` float32 ``[B, pieces, n_heads, dim, vdim]`` lets a long prompt run in pieces side by side (``pieces =
+    retention_pieces(longest sequence)``)."""
+    lib = _lib("recurrent")
+    p_n, n, width = rows.shape
+    n_seqs = slots.numel()
+    assert out.shape == (n, n_heads * vdim) and state.shape[1:] == (n_heads, dim, vdim) and decay.shape == (n_heads,)
+    for col, w_ in ((q_col, n_heads * dim), (k_col, n_heads * dim), (v_col, n_heads * vdim), (g_col, n_heads * vdim)):
+        assert 0 <= col and col + w_ <= width
+    a = _RetentionArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.row_width, a.q_col, a.k_col, a.v_col, a.g_col = width, q_col, k_col, v_col, g_col
+    if cos is not None and rotary_dim:
+        assert cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim
+        a.cos_table, a.sin_table = _ptr(cos, torch.float32), _ptr(sin, torch.float32)
+        a.rotary_dim, a.table_positions = rotary_dim, cos.shape[0]
+    a.positions, a.decay = _ptr(positions, torch.int32), _ptr(decay, torch.float32)
+    a.k_scale, a.eps = float(k_scale), float(eps)
+    a.state, a.slots, a.cu_tokens = _ptr(state, torch.float32), _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.out, a.out_dtype = _ptr(out), _dt(out)
+    max_count = 0
+    if carry is not None:
+        assert carry.dim() == 5 and carry.shape[0] >= n_seqs and carry.shape[2:] == (n_heads, dim, vdim) and carry.is_contiguous()
+        a.carry, a.pieces = _ptr(carry, torch.float32), carry.shape[1]
+        max_count = min(n, carry.shape[1] * RETENTION_PIECE)
+    a.n_seqs, a.n_tokens, a.nh, a.dim, a.vdim = n_seqs, n, n_heads, dim, vdim
+    _check(lib, lib.llg_retention(byref(a), max_count, _stream()), kernels=3 if carry is not None else 1)
+
+
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     """y[n, h, :] = w[h] x[n, h, :]: ``x`` ``[N, nh, a]``, ``w`` ``[nh, b, a]`` (contiguous), ``y`` ``[N, nh, b]``.  ``x`` and
-    ``y`` may be views into wider rows (their last elements contiguous); float32 sums, one dtype for all three.
+    ``y`` may be views into wider rows (their last elements contiguous); float32 sums; ``x`` and ``w`` share a dtype, ``y``
+    has it too or is float32 (the sums as they are).
     bfloat16 with rows on 16-byte boundaries runs on the tensor cores (csrc/moe.cu's grouped kernel), the rest on the CUDA
     cores (csrc/latent.cu)."""
     lib = _lib("latent")
@@ -906,8 +1166,8 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     assert w.shape[0] == nh and w.shape[2] == k and y.shape == (n, nh, w.shape[1]), (x.shape, w.shape, y.shape)
     if not (x.is_cuda and w.is_cuda and y.is_cuda):
         raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
-    if x.dtype != w.dtype or x.dtype != y.dtype:
-        raise KernelError("head_linear: x, w and y must share a dtype")
+    if x.dtype != w.dtype or y.dtype not in (x.dtype, torch.float32):
+        raise KernelError("head_linear: x and w must share a dtype, and y has it too or is float32")
     if n and (x.stride(2) != 1 or y.stride(2) != 1):
         raise KernelError("head_linear: the innermost elements of x and y must be contiguous")
     if n and x.dtype == torch.bfloat16:
@@ -915,14 +1175,14 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
         moe = _moe_lib()
         if moe.llg_head_linear_mma_supported(x.data_ptr(), x.stride(0), x.stride(1), _ptr(w), k):
             _check(moe, moe.llg_head_linear_mma(x.data_ptr(), x.stride(0), x.stride(1), _ptr(w), y.data_ptr(), y.stride(0),
-                                                y.stride(1), n, nh, k, w.shape[1], _stream()))
+                                                y.stride(1), n, nh, k, w.shape[1], _dt(y), _stream()))
             return
     a = _HeadLinearArgs()
     a.x, a.x_token_stride, a.x_head_stride = x.data_ptr(), x.stride(0), x.stride(1)
     a.w = _ptr(w)
     a.y, a.y_token_stride, a.y_head_stride = y.data_ptr(), y.stride(0), y.stride(1)
     a.n_tokens, a.nh, a.n_in, a.n_out = n, nh, k, w.shape[1]
-    _check(lib, lib.llg_head_linear(byref(a), _dt(x), _stream()))
+    _check(lib, lib.llg_head_linear(byref(a), _dt(x), _dt(y), _stream()))
 
 
 MOE_TILE_ROWS = 32          # rows of a tile of the experts' grouped products; checked against the library at first use
@@ -957,18 +1217,22 @@ def moe_row_capacity(pairs: int, n_experts: int, tile: int = MOE_TILE_ROWS) -> i
     return -(-cap // tile) * tile
 
 
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1, "softmax_all": 2}
+
+
 class RouterRule:
     """How logits become a token's experts and weights.  ``score`` "softmax": the ``top`` largest logits, weighted by a
-    softmax over them.  "sigmoid": scores ``s = sigmoid(logit)``; with ``groups`` the experts form that many equal groups of
+    softmax over them.  "softmax_all": scores are the softmax over every expert's logit; the ``top`` largest, weighted as
+    the sigmoid scores are.  "sigmoid": scores ``s = sigmoid(logit)``; with ``groups`` the experts form that many equal groups of
     neighbours, a group is judged by the sum of its ``group_score_top`` largest scores and only the ``keep_groups`` best
     groups' experts can be chosen; the ``top`` largest eligible scores, ``weight = s / (sum of the chosen + weight_sum_eps) *
     weight_scale``."""
 
     def __init__(self, score: str = "softmax", groups: int = 0, keep_groups: int = 0, group_score_top: int = 2,
                  weight_scale: float = 1.0, weight_sum_eps: float = 0.0):
-        if score not in ("softmax", "sigmoid"):
-            raise KernelError(f"router rule: score '{score}' is not known (softmax, sigmoid)")
-        self.c = _RouterRule(1 if score == "sigmoid" else 0, int(groups), int(keep_groups), int(group_score_top),
+        if score not in ROUTER_SCORES:
+            raise KernelError(f"router rule: score '{score}' is not known ({', '.join(ROUTER_SCORES)})")
+        self.c = _RouterRule(ROUTER_SCORES[score], int(groups), int(keep_groups), int(group_score_top),
                              float(weight_scale), float(weight_sum_eps))
 
 

@@ -21,7 +21,7 @@ import math
 import torch
 
 from ..kernels.linear import linear
-from .base import Branch, KvNeed, Mixer, TensorDecl, as_f32, register_part
+from .base import Branch, KvNeed, Mixer, MultiNeed, StateNeed, TensorDecl, as_f32, register_part
 
 
 class Attention(Mixer):
@@ -31,7 +31,11 @@ class Attention(Mixer):
     head_dim), mask ("window": the last ``window`` keys; "chunk": the keys of the query's own chunk of ``window``
     positions), sink (None or "learned": a tensor ``sink`` [num_heads]), value_blend (None, or the name of a group of
     layers that blend their values with the group's first layer's; every member has a tensor ``vmix`` [], which the
-    first does not use)."""
+    first does not use), conv_taps (0, or the taps of a short causal convolution over time on every channel of q, k and v,
+    directly behind the projections: tensors ``q_proj.conv``, ``k_proj.conv``, ``v_proj.conv`` [channels, taps], the last
+    column the current token's; the last ``taps - 1`` projected rows of a sequence are kept as float32 state beside the
+    keys and values), out_gate (False, or True: the concatenated heads are multiplied by ``sigmoid(g_proj x)`` before
+    the output projection; a tensor ``g_proj.weight`` [num_heads * value_dim, hidden])."""
 
     TAKES_ROW_SCALE = True
 
@@ -67,7 +71,18 @@ class Attention(Mixer):
         self.blend_group = p.get("value_blend")
         if self.blend_group is not None and not self.own_kv:
             raise ValueError("attention: values are blended by the layer that projects them (own_kv)")
-        self.special = self.vd != self.hd or self.mask != "window" or self.sink_kind is not None
+        self.conv_taps = int(p.get("conv_taps", 0) or 0)
+        taps_limit = getattr(env.ops, "CONV_MAX_TAPS", None)
+        if self.conv_taps < 0 or (taps_limit is not None and self.conv_taps > taps_limit):
+            raise ValueError(f"attention: {self.conv_taps} convolution taps (0 to {taps_limit})")
+        if self.conv_taps and not self.own_kv:
+            raise ValueError("attention: the convolution goes with the layer that projects its keys and values (own_kv)")
+        self.out_gate = bool(p.get("out_gate", False))
+        self.special = (self.vd != self.hd or self.mask != "window" or self.sink_kind is not None or bool(self.conv_taps)
+                        or self.out_gate)
+        self.w_gate = self.w_conv = None
+        if self.conv_taps:
+            self.TAKES_ROW_SCALE = False      # the convolution mixes rows: every row arrives finished
         self.form = None
         self.sinks = self.v_lambda = None
         scale = p.get("softmax_scale")
@@ -96,6 +111,12 @@ class Attention(Mixer):
             t["sink"] = TensorDecl((self.nh,), "bias")
         if self.blend_group is not None:
             t["vmix"] = TensorDecl((), "bias")
+        if self.conv_taps:
+            t["q_proj.conv"] = TensorDecl((q, self.conv_taps), "conv")
+            t["k_proj.conv"] = TensorDecl((kv, self.conv_taps), "conv")
+            t["v_proj.conv"] = TensorDecl((self.nkv * self.vd, self.conv_taps), "conv")
+        if self.out_gate:
+            t["g_proj.weight"] = TensorDecl((self.nh * self.vd, self.hidden))
         return t
 
     def bind(self, tensors):
@@ -117,13 +138,29 @@ class Attention(Mixer):
             self.sinks = as_f32(tensors["sink"], self.env)
         if self.blend_group is not None:
             self.v_lambda = as_f32(tensors["vmix"], self.env).reshape(1)
-        if self.special:
+        self.qkv_width = self.w_qkv.shape[0]
+        if self.conv_taps:
+            self.w_conv = torch.cat([as_f32(tensors[n + ".conv"], self.env) for n in names], dim=0).contiguous()
+        if self.out_gate:
+            self.w_gate = tensors["g_proj.weight"]
+            if self.conv_taps and self.w_gate.dtype == self.w_qkv.dtype:
+                # behind a convolution the preparation reads a buffer of its own, so the gate's rows can ride in the
+                # projections' product
+                self.w_qkv = torch.cat([self.w_qkv, self.w_gate], dim=0).contiguous()
+                self.w_gate = None
+        if self.vd != self.hd or self.mask != "window" or self.sink_kind is not None:
             self.form = self.env.ops.AttentionForm(value_dim=self.vd, sinks=self.sinks, chunked=self.mask == "chunk")
 
     def cache_need(self):
         if not self.own_kv:
             return None
-        return KvNeed(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd)
+        kv = KvNeed(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd)
+        if self.conv_taps > 1:
+            return MultiNeed.of(kv=kv, conv=StateNeed((self.conv_taps - 1, self.qkv_width_of()), torch.float32))
+        return kv
+
+    def qkv_width_of(self) -> int:
+        return (self.nh + self.nkv) * self.hd + self.nkv * self.vd
 
     def check_borrowed(self, need) -> None:
         if self.own_kv:
@@ -141,6 +178,9 @@ class Attention(Mixer):
         ops = ctx.ops
         n = x.shape[0]
         nkv_in = self.nkv if self.own_kv else 0
+        conv_state = None
+        if self.conv_taps > 1:
+            cache, conv_state = cache["kv"], cache["conv"].state
         rot = self.encoding.rotation() if self.encoding is not None else None
         # A large prompt step on the tensor cores prepares q and k in the projection's own epilogue.  Otherwise the
         # projection writes float32 (partials when the product splits K) and a second kernel prepares them; either
@@ -162,7 +202,7 @@ class Attention(Mixer):
                 if tuple(lent.shape) != (n, self.nkv, self.vd):
                     raise ValueError(f"attention: layers of the value group '{self.blend_group}' differ in their values' shape")
                 extra["v_first_in"], extra["v_mix"] = lent, self.v_lambda
-        if (not ctx.decode and fused_qkv is not None and not extra
+        if (not ctx.decode and fused_qkv is not None and not extra and not self.conv_taps and not self.out_gate
                 and fused_qkv(x, self.w_qkv, self.hd, rot.rotary_dim if rot else 0, rot.pairing if rot else 0)):
             def prep(qkv_, **kw):
                 ops.gemm_tc_qkv(x, self.w_qkv, **kw, **scale_kw)
@@ -171,6 +211,21 @@ class Attention(Mixer):
             def prep(qkv_, **kw):
                 ops.qk_prep(qkv_, **kw, **scale_kw, **extra)
             qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32)
+        gate, gate_col = None, 0
+        if self.out_gate:
+            if self.w_gate is None:
+                gate, gate_col = qkv, self.qkv_width                 # the gate's arguments lie behind q, k, v in the same rows
+            else:
+                gate = linear(ctx, x, self.w_gate, "attn.gate", torch.float32)
+        if self.conv_taps:
+            # the convolution sees the projections' float32 sums (times the row scale's factor: it is linear) and leaves
+            # one set of float32 rows of q | k | v for the preparation
+            if row_scale is not None:
+                raise ValueError("attention: a convolution behind the projections takes finished rows (no row scale)")
+            mixed = ctx.buffer("attn.conv", (1, n, self.qkv_width), torch.float32)
+            ops.causal_conv(qkv, 0, self.w_conv, conv_state, ctx.slots, ctx.cu_tokens, ctx.seq_of_token, ctx.len_before,
+                            mixed[0])
+            qkv = mixed
         q = ctx.buffer("attn.q", (n, self.nh, self.hd))
         out = ctx.buffer("attn.out", (n, self.nh * self.vd))
         common = dict(n_heads=self.nh, n_kv_heads=nkv_in, head_dim=self.hd,
@@ -227,6 +282,8 @@ class Attention(Mixer):
                     cache.shared.setdefault("after_last_reader", []).append(write_ring)
                 else:
                     write_ring()
+        if gate is not None:
+            ops.sigmoid_gate(out, gate, gate_col)
         return Branch(linear(ctx, out, self.w_o, "attn.proj", torch.float32))
 
 

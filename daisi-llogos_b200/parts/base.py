@@ -35,8 +35,20 @@ class TensorDecl:
     """A tensor a part needs: its shape and what it is (decides random initialisation)."""
 
     shape: Tuple[int, ...]
-    role: str = "matrix"       # "matrix" | "norm" | "bias" | "table" | "stream_gain" | "stream_mix"
+    role: str = "matrix"       # "matrix" | "norm" | "bias" | "table" | "stream_gain" | "stream_mix" | "conv" | "rate"
     optional: bool = False
+
+
+@dataclass(frozen=True)
+class Term:
+    """One summand of what enters the residual: float32 partials ``[S, N, H]``; with ``weight`` (float32 ``[H]``) their sum
+    is divided by its own root mean square (``eps`` inside the root) and multiplied by that weight first; ``scale`` times
+    the result is added."""
+
+    data: torch.Tensor
+    weight: Optional[torch.Tensor] = None
+    eps: float = 0.0
+    scale: float = 1.0
 
 
 @dataclass
@@ -48,18 +60,35 @@ class Branch:
     more than one stream, the part that holds the weights with which this branch enters the streams (set by the
     block that arranged the sublayer; ``None`` where the branch is simply added).  ``more``: further sets of
     partials ``[s_i, n_tokens, hidden]`` that enter the residual together with ``data`` (sublayers that read the
-    same norm's output side by side); ``scale``: the factor on the whole sum as it is added.  Only norms that say
-    so take ``more`` or a scale other than 1 (``Norm.check_plain`` is for the others).
+    same norm's output side by side); ``scale``: the factor on the whole sum as it is added.  ``terms``: instead of all
+    that, the summands one by one (``Term``), each with a norm and a factor of its own; ``data`` is then the first term's.
+    Only norms that say so take ``more``, a scale other than 1 or terms (``Norm.check_plain`` is for the others).
     """
 
     data: torch.Tensor
     write: Any = None
     more: Tuple[torch.Tensor, ...] = ()
     scale: float = 1.0
+    terms: Tuple[Term, ...] = ()
 
     @property
     def n_partials(self) -> int:
         return self.data.shape[0]
+
+    @classmethod
+    def of_terms(cls, terms) -> "Branch":
+        terms = tuple(terms)
+        if not terms:
+            raise ValueError("a branch needs at least one term")
+        return cls(terms[0].data, terms=terms)
+
+    def as_terms(self) -> Tuple[Term, ...]:
+        """The branch as a list of summands, whichever way it was built (``write`` has no such reading)."""
+        if self.write is not None:
+            raise ValueError("a branch that enters the residual through a part of its own has no plain terms")
+        if self.terms:
+            return self.terms
+        return tuple(Term(d, scale=self.scale) for d in (self.data,) + tuple(self.more))
 
 
 @dataclass(frozen=True)
@@ -81,6 +110,20 @@ class StateNeed:
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class MultiNeed:
+    """A part keeps several things per sequence: ``needs`` is ``((name, need), ...)`` with each need a ``KvNeed``, a
+    ``StateNeed`` or another ``MultiNeed``.  The cache hands the part a ``MultiView`` whose ``[name]`` is the view of that
+    need."""
+
+    needs: Tuple[Tuple[str, Any], ...]
+
+    @classmethod
+    def of(cls, **needs) -> Optional["MultiNeed"]:
+        kept = tuple((k, v) for k, v in needs.items() if v is not None)
+        return cls(kept) if kept else None
 
 
 class Part:
@@ -127,7 +170,7 @@ class Norm(Part):
     @staticmethod
     def check_plain(branch: Optional[Branch], who: str) -> None:
         """For norms that add one set of partials, unscaled: refuses a branch that asks for more."""
-        if branch is not None and (branch.more or branch.scale != 1.0):
+        if branch is not None and (branch.more or branch.scale != 1.0 or branch.terms):
             raise ValueError(f"{who}: the pending branch carries several sublayers' outputs or a scale; "
                              f"this norm adds one output as it is")
 

@@ -55,6 +55,45 @@ class ParallelBlock(Block):
         return Branch(a.data, more=(f.data,) + tuple(f.more), scale=self.scale)
 
 
+class TwoNormParallelBlock(Block):
+    """Mixer and feed-forward side by side, each behind a norm of its own over the SAME residual, and an optional last
+    sublayer that reads the residual once both have been added:
+
+        x' = x + mixer(norm1(x)) + ffn(norm2(x));     x'' = x' + side(x')
+
+    roles: norm1, mixer, and optionally norm2 + ffn and side (family "connection": a part with
+    ``forward(residual, pending, ctx) -> Branch`` that adds the pending branch itself, because it reads the sum).  Both
+    norms run in one launch (``norm1.forward_many``), which also adds the branch the block before left pending.  The
+    sublayers' branches may be several terms with norms and factors of their own; they are handed on as one branch of
+    terms, so the norm that adds them must take terms."""
+
+    ROLES = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "ffn": "ffn", "side": "connection"}
+
+    def __init__(self, params, prefix, env, parts):
+        super().__init__(params, prefix, env, parts)
+        for role in ("norm1", "mixer"):
+            if role not in parts:
+                raise ValueError(f"two-norm parallel block: no part for the role '{role}'")
+        if ("ffn" in parts) != ("norm2" in parts):
+            raise ValueError("two-norm parallel block: norm2 and ffn come together or not at all")
+        if not hasattr(parts["norm1"], "forward_many"):
+            raise ValueError("two-norm parallel block: norm1 must be a norm that can share its launch (rmsnorm)")
+
+    def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
+        p = self.parts
+        if "ffn" in p:
+            h1, h2 = p["norm1"].forward_many(residual, pending, ctx, (p["norm2"],))
+        else:
+            (h1,) = p["norm1"].forward_many(residual, pending, ctx, ())
+        terms = p["mixer"].forward(h1, ctx, cache).as_terms()
+        if "ffn" in p:
+            terms = terms + p["ffn"].forward(h2, ctx).as_terms()
+        out = Branch.of_terms(terms)
+        if "side" in p:
+            out = p["side"].forward(residual, out, ctx)
+        return out
+
+
 def normed_for(norm, consumer, residual, pending, ctx, rows=None):
     """``(x, keyword arguments)`` for ``consumer.forward``: a consumer that takes a row scale lets the norm leave
     its division to the consumer's first product."""
@@ -66,3 +105,4 @@ def normed_for(norm, consumer, residual, pending, ctx, rows=None):
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "parallel", ParallelBlock)
+register_part("block", "two_norm_parallel", TwoNormParallelBlock)

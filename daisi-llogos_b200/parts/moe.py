@@ -1,7 +1,8 @@
 """A feed-forward of many small experts of which every token uses a few, beside an optional shared expert.
 
 Router: ``z = W_r h + b`` with float32 sums; the ``top`` experts of largest ``z`` are chosen per token and weighted by a
-softmax over the chosen logits alone.  Or, by parameter (``score = "sigmoid"``): every expert's score is ``s = sigmoid(z)``; the
+softmax over the chosen logits alone.  Or (``score = "softmax_all"``) the scores are the softmax over ALL experts' logits,
+the ``top`` largest are chosen and weighted by ``s / (sum of the chosen s + weight_sum_eps) * weight_scale``.  Or, by parameter (``score = "sigmoid"``): every expert's score is ``s = sigmoid(z)``; the
 experts form ``groups`` equal groups of neighbours, a group is judged by the sum of its ``group_score_top`` largest scores,
 and only the experts of the ``keep_groups`` best groups can be chosen; the ``top`` eligible experts of largest score are
 weighted by ``s / (sum of the chosen s + weight_sum_eps) * weight_scale``.  Every expert is the gated form ``W_down (silu(W_gate h) * W_up h)`` without
@@ -27,7 +28,7 @@ from .base import Branch, FeedForward, TensorDecl, as_f32, part_class, register_
 class MoeFeedForward(FeedForward):
     """params: hidden_size, num_experts, top, expert_size (an expert's inner size), shared_size (0 or None: no shared
     expert), router_bias (bool), shared_prefix (where the shared expert's tensors lie under this part's prefix,
-    default "shared."), shared_names (its ``tensor_names``), score ("softmax", the default, or "sigmoid"), groups and
+    default "shared."), shared_names (its ``tensor_names``), score ("softmax", the default, "softmax_all" or "sigmoid"), groups and
     keep_groups (0: every expert is eligible), group_score_top (default 2), weight_scale (default 1), weight_sum_eps
     (default 0), shared_gate (bool: a tensor ``shared_gate.weight`` [1, hidden]).  Tensors: ``router.weight`` [experts, hidden],
     ``router.bias`` [experts], and per expert i ``experts.<i>.{gate_proj,up_proj,down_proj}.weight``."""
@@ -49,8 +50,8 @@ class MoeFeedForward(FeedForward):
             raise ValueError(f"moe: top {self.top}; the routing kernels take up to {top_limit}")
         self.router_bias = bool(p.get("router_bias", False))
         self.score = str(p.get("score", "softmax"))
-        if self.score not in ("softmax", "sigmoid"):
-            raise ValueError(f"moe: score '{self.score}' is not known (softmax, sigmoid)")
+        if self.score not in ("softmax", "sigmoid", "softmax_all"):
+            raise ValueError(f"moe: score '{self.score}' is not known (softmax, sigmoid, softmax_all)")
         self.groups, self.keep_groups = int(p.get("groups") or 0), int(p.get("keep_groups") or 0)
         if self.groups:
             if self.score != "sigmoid":

@@ -16,11 +16,17 @@ from typing import Optional
 
 import torch
 
-from .base import Branch, Norm, TensorDecl, register_part
+from .base import Branch, Norm, TensorDecl, as_f32, register_part
 
 
 class RmsNorm(Norm):
-    """params: size, eps."""
+    """params: size, eps, weight_offset (default 0; 1 for a weight that holds its difference from one: the row is multiplied by
+    ``1 + weight``), out_name (the workspace buffer of the output, default "norm.out": two norms whose outputs are alive
+    together name two).
+
+    With ``weight_offset`` the norm runs on ``ops.multi_add_rmsnorm``, which also takes a pending branch of several
+    terms, each with a norm and a factor of its own (``Branch.terms``), and can norm the same row for a second norm in
+    the same launch (``forward_many``).  Without it everything is as before."""
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -28,15 +34,38 @@ class RmsNorm(Norm):
         self.eps = float(params["eps"])
         if self.eps <= 0:
             raise ValueError("RMSNorm eps must be positive")
+        self.weight_offset = float(params.get("weight_offset", 0.0) or 0.0)
+        self.out_name = str(params.get("out_name", "norm.out"))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self):
-        return {"weight": TensorDecl((self.size,), "norm")}
+        # such a weight is drawn near zero
+        return {"weight": TensorDecl((self.size,), "bias" if self.weight_offset else "norm")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = as_f32(tensors["weight"], self.env) if self.weight_offset else tensors["weight"]
+
+    def forward_many(self, residual, branch: Optional[Branch], ctx, others=(), rows=None):
+        """Adds the pending branch and norms the sum for this norm and for ``others`` (norms of the same size and eps
+        with weights of their own) in one launch; returns the outputs in that order."""
+        norms = (self,) + tuple(others)
+        for o in norms:
+            if not isinstance(o, RmsNorm) or o.size != self.size or o.eps != self.eps:
+                raise ValueError("rmsnorm: norms that share a launch share their size and eps")
+        m = residual.shape[0] if rows is None else rows.numel()
+        names = [o.out_name for o in norms]
+        if len(set(names)) != len(names):
+            raise ValueError(f"rmsnorm: norms that share a launch write to buffers of their own (out_name), got {names}")
+        outs = [ctx.buffer(o.out_name, (m, self.size)) for o in norms]
+        terms = () if branch is None else branch.as_terms()
+        ws = [o.weight if o.weight.dtype == torch.float32 else as_f32(o.weight, self.env) for o in norms]
+        ctx.ops.multi_add_rmsnorm(residual, [(t.data, t.weight, t.eps, t.scale) for t in terms],
+                                  [(out, w, o.weight_offset) for out, w, o in zip(outs, ws, norms)], self.eps, rows)
+        return outs
 
     def forward(self, residual, branch: Optional[Branch], ctx, rows=None):
+        if self.weight_offset or (branch is not None and branch.terms):
+            return self.forward_many(residual, branch, ctx, (), rows)[0]
         self.check_plain(branch, "rmsnorm")
         m = residual.shape[0] if rows is None else rows.numel()
         out = ctx.buffer("norm.out", (m, self.size))
@@ -46,7 +75,7 @@ class RmsNorm(Norm):
     def forward_unscaled(self, residual, branch: Optional[Branch], ctx, rows=None):
         ops = ctx.ops
         make_scale = getattr(ops, "RowScale", None)
-        if make_scale is None or ctx.dtype != torch.bfloat16:
+        if make_scale is None or ctx.dtype != torch.bfloat16 or self.weight_offset or (branch is not None and branch.terms):
             return self.forward(residual, branch, ctx, rows), None
         self.check_plain(branch, "rmsnorm")
         m = residual.shape[0] if rows is None else rows.numel()

@@ -139,7 +139,7 @@ def _to_device(t: torch.Tensor, device: torch.device, compute: torch.dtype, ops)
 def random_tensors(decls, seed: int, *, std: float = 0.02, norm_std: float = 0.0, bias_std: float = 0.02,
                    dtype: torch.dtype = torch.bfloat16, device="cpu", ops=None) -> Dict[str, torch.Tensor]:
     """One tensor per declaration: matrices and tables N(0, std), norm weights 1 + N(0, norm_std),
-    biases N(0, bias_std).  Every element is a function of (seed, tensor name, element index) alone
+    biases N(0, bias_std), the taps of short convolutions N(0, 1/2), the rates of a recurrence's decay N(-3, 1).  Every element is a function of (seed, tensor name, element index) alone
     (weights/random_init.py), so the values do not depend on the device that makes them: on the GPU the
     library's fill kernel writes them, on the CPU numpy does."""
     device = torch.device(device)
@@ -150,7 +150,8 @@ def random_tensors(decls, seed: int, *, std: float = 0.02, norm_std: float = 0.0
         # norm weights and the gains of residual streams scatter around 1, a stream-mixing matrix around the identity
         near_one = d.role in ("norm", "stream_gain")
         mean, spread = (1.0, norm_std) if near_one else (0.0, bias_std) if d.role == "bias" else \
-            (0.0, norm_std) if d.role == "stream_mix" else (0.0, std)
+            (0.0, norm_std) if d.role == "stream_mix" else (0.0, 0.5) if d.role == "conv" else \
+            (-3.0, 1.0) if d.role == "rate" else (0.0, std)
         t = torch.empty(d.shape, dtype=dtype, device=device)
         fill_normal(t, tensor_key(seed, name), mean, spread, ops)
         if d.role == "stream_mix":

@@ -214,6 +214,127 @@ def mingru_scan(rows, bias, state, slots, cu_tokens, out, carry=None):
         state[int(slots[b])] = s
 
 
+def multi_add_rmsnorm(residual, terms, outs, eps, rows=None):
+    idx = slice(None) if rows is None else rows.long()
+    for data, w, w_eps, scale in terms:
+        y = data.float().sum(0)[idx]
+        if w is not None:
+            y = y * torch.rsqrt((y * y).mean(-1, keepdim=True) + w_eps) * w.float()
+        residual[idx] += scale * y
+    x = residual[idx]
+    inv = torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+    for out, w, offset in outs:
+        out.copy_((x if w is None else x * inv * (offset + w.float())).to(out.dtype))
+
+
+def hash_embed(table, scale, pair_table, buckets, mul_prev, mul_cur, token_ids, positions, seq_of_token, cu_tokens, slots,
+               last_token, norm_w, norm_offset, eps, out_residual):
+    tok = token_ids.long()
+    x = table[tok].float() * scale
+    if pair_table is not None:
+        rows = torch.empty_like(tok)
+        for n in range(tok.numel()):
+            b = int(seq_of_token[n])
+            if int(positions[n]) == 0:
+                rows[n] = buckets
+                continue
+            prev = int(tok[n - 1]) if n > int(cu_tokens[b]) else int(last_token[int(slots[b]), 0])
+            rows[n] = (prev * mul_prev + int(tok[n]) * mul_cur) % buckets
+        for b in range(slots.numel()):
+            last_token[int(slots[b]), 0] = int(tok[int(cu_tokens[b + 1]) - 1])
+        x = x + pair_table[rows].float()
+    if norm_w is not None:
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * (norm_offset + norm_w.float())
+    out_residual.copy_(x)
+
+
+def table_gate(rows, table, col0, token_ids, out, kind):
+    z = rows.float().sum(0)
+    e = table[token_ids.long()][:, col0:col0 + z.shape[1]].float()
+    out.copy_((_act(z, kind) * e).to(out.dtype))
+
+
+def _act(z, kind):
+    if kind == "relu2":
+        return torch.relu(z) ** 2
+    if kind == "gelu_tanh":
+        return 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    if kind == "silu":
+        return z * torch.sigmoid(z)
+    return torch.relu(z)
+
+
+CONV_MAX_TAPS = 16
+RETENTION_PIECE = 4
+
+
+def causal_conv(rows, col0, weight, state, slots, cu_tokens, seq_of_token, len_before, out, in_bias=None, bias=None, out2=None):
+    c, k = weight.shape
+    x = rows.float().sum(0)[:, col0:col0 + c]
+    if in_bias is not None:
+        x = x + in_bias.float()
+    for b in range(slots.numel()):
+        t0, t1 = int(cu_tokens[b]), int(cu_tokens[b + 1])
+        past = state[int(slots[b])].float() if k > 1 else x.new_zeros((0, c))
+        seq = torch.cat([past, x[t0:t1]])               # the state holds zeros where the sequence had not begun
+        for t in range(t1 - t0):
+            y = (seq[t:t + k] * weight.float().t()).sum(0)
+            out[t0 + t] = y if bias is None else y + bias.float()
+        if k > 1:
+            state[int(slots[b])] = seq[seq.shape[0] - (k - 1):]
+    if out2 is not None:
+        out2.copy_(out.to(out2.dtype))
+
+
+def rglru_scan(rows, y_col, y_bias, u, gates, gate_bias, lam, decay_scale, state, slots, cu_tokens, out, carry=None):
+    n, size = out.shape
+    bw = gates.shape[2] // 2
+    y = rows.float().sum(0)[:, y_col:y_col + size]
+    if y_bias is not None:
+        y = y + y_bias.float()
+    g = gates.float() + gate_bias.float()
+    r = torch.sigmoid(g[:, :, :bw]).reshape(n, size)
+    i = torch.sigmoid(g[:, :, bw:]).reshape(n, size)
+    a = torch.exp(-decay_scale * r * torch.nn.functional.softplus(lam.float()))
+    drive = torch.sqrt(1 - a * a) * i * u.float()
+    for b in range(slots.numel()):
+        s = state[int(slots[b])].clone()
+        for t in range(int(cu_tokens[b]), int(cu_tokens[b + 1])):
+            s = a[t] * s + drive[t]
+            out[t] = (s * _act(y[t], "gelu_tanh")).to(out.dtype)
+        state[int(slots[b])] = s
+
+
+def retention_pieces(max_count):
+    return -(-max_count // RETENTION_PIECE)
+
+
+def retention(rows, *, q_col, k_col, v_col, g_col, n_heads, dim, vdim, cos, sin, rotary_dim, positions, decay, k_scale, eps,
+              state, slots, cu_tokens, out, carry=None):
+    x = rows.float().sum(0)
+    n = x.shape[0]
+    q = x[:, q_col:q_col + n_heads * dim].reshape(n, n_heads, dim).clone()
+    k = x[:, k_col:k_col + n_heads * dim].reshape(n, n_heads, dim).clone()
+    v = x[:, v_col:v_col + n_heads * vdim].reshape(n, n_heads, vdim)
+    g = x[:, g_col:g_col + n_heads * vdim].reshape(n, n_heads, vdim)
+    if cos is not None and rotary_dim:
+        half = rotary_dim // 2
+        c, s = cos[positions.long()][:, None, :], sin[positions.long()][:, None, :]
+        for t in (q, k):
+            a, b2 = t[..., :half].clone(), t[..., half:rotary_dim].clone()
+            t[..., :half] = a * c - b2 * s
+            t[..., half:rotary_dim] = b2 * c + a * s
+    k = k * k_scale
+    for b in range(slots.numel()):
+        st = state[int(slots[b])].clone()
+        for t in range(int(cu_tokens[b]), int(cu_tokens[b + 1])):
+            st = decay.float()[:, None, None] * st + k[t][:, :, None] * v[t][:, None, :]
+            o = torch.einsum("hdv,hd->hv", st, q[t])
+            o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * (g[t] * torch.sigmoid(g[t]))
+            out[t] = o.reshape(-1).to(out.dtype)
+        state[int(slots[b])] = st
+
+
 def tanh_cap(x, cap):
     x.copy_(cap * torch.tanh(x / cap))
 
@@ -255,7 +376,7 @@ def moe_route(x, w_router, b_router, choice, weight, rule=None, extra_out=None):
         choice.copy_(idx.to(torch.int32))
         weight.copy_(torch.softmax(val, dim=-1))
         return
-    s = torch.sigmoid(z)
+    s = torch.softmax(z, dim=-1) if rule.score == "softmax_all" else torch.sigmoid(z)
     n, n_exp = s.shape
     masked = s
     if rule.groups:
