@@ -365,7 +365,8 @@ __global__ void __launch_bounds__(RET_THREADS) retention_kernel(RetentionArgs a)
       if (MODE != 1) sg[j] = summed(a.g_col + h * vdim + j);
     }
     __syncthreads();
-    for (int j = tj; j < vdim; j += cols) {
+    // threads beyond slices * cols (where the block's size is no multiple of cols) have no share of the state
+    for (int j = sl < slices ? tj : vdim; j < vdim; j += cols) {
       const float vj = sv[j];
       float o = 0.f;
       for (int i = sl; i < dim; i += slices) {
