@@ -178,13 +178,17 @@ def expert(h, w, p):
 
 
 def route(h, w, p, router: dict):
-    """(chosen experts [T, top], weights [T, top], margin [T]: by how much the last chosen score beats the next)."""
+    """(chosen experts [T, top], weights [T, top], margin [T]): the margin is by how much the last chosen score beats the
+    next, as a share of the chosen scores' sum; infinite where nothing is left out, or where the last chosen expert's
+    share of the sum is below 1/100 (then it hardly matters which of the two is taken)."""
     top = int(router["top"])
     s = torch.softmax(linear(h, w[p + "router"]), dim=-1)
     val, idx = torch.topk(s, top, dim=-1)
     margin = torch.full((s.shape[0],), math.inf, dtype=F64)
     if top < s.shape[1]:
-        margin = val[:, -1] - torch.topk(s, top + 1, dim=-1).values[:, -1]
+        total = val.sum(-1)
+        margin = (val[:, -1] - torch.topk(s, top + 1, dim=-1).values[:, -1]) / total
+        margin = torch.where(val[:, -1] / total < 0.01, torch.full_like(margin, math.inf), margin)
     weights = val / (val.sum(-1, keepdim=True) + 1e-20) * float(router.get("scale", 1.0))
     return idx, weights, margin
 
