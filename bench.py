@@ -25,7 +25,9 @@ sizes (``--sizes``), prompt and decode throughput of each and every kernel of th
 ``--design fipavik`` puts the Fipavik design (latent and chunked attention, a mixture of experts whose active size is the
 stock model's feed-forward) in Karitar's place; ``--design rukedra`` puts the Rukedra design (two kinds of latent attention
 and a minGRU mixer between grouped norms with gated residuals, dense and mixture feed-forwards in turn) beside Fipavik, the
-closest model the library has, at equal latent, expert and feed-forward sizes.
+closest model the library has, at equal latent, expert and feed-forward sizes; ``--design piratar`` puts the Piratar design
+(softmax attention with short convolutions beside retention, an RG-LRU block, two norms over one residual, a per-token
+input) beside Rukedra at equal widths, experts and feed-forward sizes.
 """
 import argparse
 import json
@@ -412,6 +414,30 @@ def rukedra_config(size):
             "logit_softcap": 30.0, "layers": layers}
 
 
+def piratar_config(size):
+    """Piratar at a size, four layers: attention beside retention with a dense feed-forward, an RG-LRU block with a mixture,
+    attention beside retention with a dense feed-forward, attention beside retention with a mixture.  The attention side
+    has the stock model's heads (values of the keys' size, four taps behind q, k and v, every element rotated), the
+    retention side a quarter as many heads of the same size, the recurrent block is as wide as the model in sixteen
+    blocks; the experts (sixteen, four per token, a shared expert) are Rukedra's at this size, the dense feed-forward
+    the stock model's; a pair table of 100,003 rows and a per-token input of 64 elements a layer."""
+    width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
+    rot = {"base": 1000000.0, "dims": hd}
+    le = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "conv": 4, "rot": dict(rot)}
+    r_heads = max(1, heads // 4)
+    ri = {"heads": r_heads, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + (i % 6)) for i in range(r_heads)], "rot": dict(rot)}
+    par = {"type": "parallel", "mixer": {"left": le, "right": ri}}
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": 16, "conv": 4}}
+    moe = {"kind": "moe", "router": {"experts": FIPAVIK_EXPERTS, "top": FIPAVIK_TOP, "scale": 2.5}, "expert": {"ff": ff // 8},
+           "shared": {"ff": ff // 2}}
+    dense = {"kind": "dense", "ff": ff}
+    layers = [dict(par, mlp=dict(dense)), dict(rec, mlp=dict(moe)), dict(par, mlp=dict(dense)), dict(par, mlp=dict(moe))]
+    assert len(layers) == DESIGN_LAYERS
+    return {"architecture": "Piratar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 17}},
+            "token_side": {"dim": 64}, "layers": layers}
+
+
 def design_configs(size, design="karitar"):
     """The configuration of ``design`` (Karitar or Fipavik) at a size and the closest stock model's (Qwen3: grouped-query
     attention with normed queries and keys and the same window, pre-norm blocks) with the same width, heads, head size
@@ -432,13 +458,20 @@ def design_configs(size, design="karitar"):
         return {"fipavik": fipavik_config(size), "qwen3": qwen3}
     if design == "rukedra":
         return {"rukedra": rukedra_config(size), "fipavik": fipavik_config(size)}
+    if design == "piratar":
+        return {"piratar": piratar_config(size), "rukedra": rukedra_config(size)}
     return {"karitar": karitar, "qwen3": qwen3}
 
 
 _TIMED_OPS = ("embed_rows", "add_rmsnorm", "hc_add_rmsnorm", "qk_prep", "qkv_row_prep", "gemm_tc", "gemm_tc_act", "gemm_tc_qkv",
               "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write", "add_layernorm", "latent_prep", "head_linear",
               "moe_route", "moe_topk", "moe_plan", "moe_gather_rows", "moe_gated", "moe_down", "moe_combine",
-              "gated_add_group_rmsnorm", "mingru_scan", "sigmoid_gate", "tanh_cap")
+              "gated_add_group_rmsnorm", "mingru_scan", "sigmoid_gate", "tanh_cap", "multi_add_rmsnorm", "hash_embed",
+              "table_gate", "causal_conv", "rglru_scan", "retention")
+
+# What the float32 multiply-adds of a B200's CUDA cores can do at most (148 multiprocessors x 128 lanes x 2 flops at
+# 1.9 GHz): the arithmetic bound of kernels whose products must stay float32 (retention's state).
+FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12
 
 
 def _kernel_label(name, args, kw):
@@ -448,6 +481,9 @@ def _kernel_label(name, args, kw):
         what = "gated" if kw.get("gated_features") else "act" if name == "gemm_tc_act" else "qkv+prep" if name == "gemm_tc_qkv" else ""
         return f"product {k}->{o} {what}".strip()
     return name
+
+
+_TENSOR_PER_FP32 = [1.0]     # set by probe_designs: the measured matrix peak over FP32_TFLOPS
 
 
 def _kernel_cost(name, args, kw, keys_read):
@@ -485,6 +521,36 @@ def _kernel_cost(name, args, kw, keys_read):
         m, h = out.shape
         per_row = 4 * h * (2 if branch is not None else 1) + 4 * h * sum(t.shape[0] for t in (branch, gate) if t is not None)
         return m * (per_row + h * out.element_size()), 0.0
+    if name == "multi_add_rmsnorm":
+        residual, terms, outs = args[0], args[1], args[2]
+        m, h = outs[0][0].shape
+        per_row = 4 * h * (2 if terms else 1) + 4 * h * sum(t[0].shape[0] for t in terms) + sum(h * o[0].element_size() for o in outs)
+        return m * per_row, 0.0
+    if name == "hash_embed":
+        table, out = args[0], args[15]
+        return out.shape[0] * out.shape[1] * (4 + table.element_size() * (2 if args[2] is not None else 1)), 0.0
+    if name == "table_gate":
+        rows, table, out = args[0], args[1], args[4]
+        return rows.nbytes + out.nbytes + out.numel() * table.element_size(), 0.0
+    if name == "causal_conv":
+        rows, weight, out = args[0], args[2], args[8]
+        out2 = kw.get("out2")
+        return rows.shape[0] * out.numel() * 4 + out.nbytes + (out2.nbytes if out2 is not None else 0), 0.0
+    if name == "rglru_scan":
+        # y's partial sums, u, the gates' arguments and the outputs; with the scan in pieces u and the gates are read twice
+        rows, u, gates, out = args[0], args[3], args[4], args[11]
+        carry = args[12] if len(args) > 12 else kw.get("carry")
+        return rows.shape[0] * out.numel() * 4 + (u.nbytes + gates.nbytes) * (2 if carry is not None else 1) + out.nbytes, 0.0
+    if name == "retention":
+        # the step's q, k, v and gate sums, the outputs, and every sequence's state in and out; the float32 products of
+        # the state's update and read-out (in pieces: done twice) against the CUDA cores' peak, counted as that many
+        # tensor-core flops so that the table's one arithmetic bound serves
+        rows, out, state = args[0], kw["out"], kw["state"]
+        carry = kw.get("carry")
+        n, nh, dim, vdim = out.shape[0], kw["n_heads"], kw["dim"], kw["vdim"]
+        moved = rows.nbytes * (2 if carry is not None else 1) + out.nbytes + 2 * kw["slots"].numel() * state[0].numel() * 4
+        flops = 4.0 * n * nh * dim * vdim * (2 if carry is not None else 1)
+        return moved, flops * _TENSOR_PER_FP32[0]
     if name == "sigmoid_gate":
         x, gate = args[0], args[1]
         return 2 * x.nbytes + gate.shape[0] * x.numel() * 4, 0.0
@@ -518,6 +584,7 @@ def probe_designs(torch, L, ops, pk, sizes, batch, which="karitar"):
     """Prefill and decode throughput of a design (``which``) beside the closest stock model at equal layer sizes, and every kernel of
     the two steps against its roofline (the slower of bytes / copy bandwidth and flops / matrix peak)."""
     os.environ["LLOGOS_RUNNER"] = "0"           # the parts call the kernels one by one, so each call can be timed
+    _TENSOR_PER_FP32[0] = pk["bf16_tflops"] / FP32_TFLOPS
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     gen = torch.Generator().manual_seed(1)
@@ -643,7 +710,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --probe timeline: the time line of a prompt step of so many tokens instead of a decode step")
     ap.add_argument("--sizes", default=",".join(DESIGN_SIZES), help="with --probe designs: which of " + ", ".join(DESIGN_SIZES))
-    ap.add_argument("--design", choices=["karitar", "fipavik", "rukedra"], default="karitar",
+    ap.add_argument("--design", choices=["karitar", "fipavik", "rukedra", "piratar"], default="karitar",
                     help="with --probe designs: the design that stands beside the closest stock model")
     ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline", "designs"],
                     help="instead of the bench line, print a table: decode attention alone over batch shapes; what "

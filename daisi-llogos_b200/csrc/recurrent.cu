@@ -400,6 +400,137 @@ __global__ void __launch_bounds__(RET_THREADS) retention_kernel(RetentionArgs a)
     for (int e = threadIdx.x; e < nst; e += RET_THREADS) cr[e] = S[e];
 }
 
+// The same walk with the state in registers and the tokens taken RET_BATCH at a time: the batch's q, k (rotated), v and
+// gate arguments are summed into shared memory together, so that no token waits for memory on its own; a thread owns
+// column j of the state's rows sl, sl + slices, ... (R of them at most), so the walk through a batch needs no barrier;
+// every token's partial read-outs (one per slice) are left in shared memory and the batch's unit norms and gates are
+// done together, a warp per token.  For value heads of up to RET_THREADS elements and R rows a thread.
+constexpr int RET_BATCH = 16;
+
+template <typename OT, int MODE, int R>
+__global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float smem[];
+  const int h = blockIdx.x, piece = blockIdx.y, b = blockIdx.z;
+  const int dim = a.dim, vdim = a.vdim, nst = dim * vdim;
+  const int slices = RET_THREADS / vdim;
+  const bool active = threadIdx.x < slices * vdim;
+  const int sl = threadIdx.x / vdim, j = threadIdx.x - sl * vdim;
+  float* sq = smem;                          // [RET_BATCH][dim]
+  float* sk = sq + RET_BATCH * dim;          // [RET_BATCH][dim]
+  float* sv = sk + RET_BATCH * dim;          // [RET_BATCH][vdim]
+  float* sg = sv + RET_BATCH * vdim;         // [RET_BATCH][vdim]
+  float* po = sg + RET_BATCH * vdim;         // [RET_BATCH][slices][vdim]
+  const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
+  int lo = t_begin, hi = t_end;
+  if (MODE != 0) {
+    lo = t_begin + piece * LLG_RETENTION_PIECE;
+    if (lo > t_end) lo = t_end;
+    hi = (piece == a.pieces - 1 || lo + LLG_RETENTION_PIECE > t_end) ? t_end : lo + LLG_RETENTION_PIECE;
+  }
+  float* gstate = a.state + ((long long)a.slots[b] * a.nh + h) * nst;
+  float* cr = MODE != 0 ? a.carry + (((long long)b * a.pieces + piece) * a.nh + h) * nst : nullptr;
+  if (MODE == 2 && lo >= hi) return;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = sl + r * slices;
+    S[r] = (active && i < dim && MODE != 1) ? (MODE == 0 ? gstate : cr)[i * vdim + j] : 0.f;
+  }
+  const float decay = a.decay[h];
+  const int rd = a.cos_table ? a.rotary_dim : 0, half = rd / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  OT* out = (OT*)a.out;
+  for (int n0 = lo; n0 < hi; n0 += RET_BATCH) {
+    const int nb = hi - n0 < RET_BATCH ? hi - n0 : RET_BATCH;
+    for (int idx = threadIdx.x; idx < nb * dim; idx += RET_THREADS) {
+      const int t = idx / dim, i = idx - t * dim;
+      const float* row = a.rows + (long long)(n0 + t) * a.row_width;
+      auto summed = [&](int col) {
+        float v = row[col];
+        for (int s = 1; s < a.n_partials; ++s) v += row[s * a.partial_stride + col];
+        return v;
+      };
+      float kv = summed(a.k_col + h * dim + i);
+      float qv = MODE != 1 ? summed(a.q_col + h * dim + i) : 0.f;
+      if (i < rd) {
+        int pos = a.positions[n0 + t];
+        if (pos >= a.table_positions) pos = a.table_positions - 1;
+        const int f = i < half ? i : i - half;
+        const int ip = i < half ? i + half : i - half;
+        const float c = a.cos_table[(long long)pos * half + f], sn = a.sin_table[(long long)pos * half + f];
+        const float kp = summed(a.k_col + h * dim + ip);
+        kv = i < half ? kv * c - kp * sn : kv * c + kp * sn;
+        if (MODE != 1) {
+          const float qp = summed(a.q_col + h * dim + ip);
+          qv = i < half ? qv * c - qp * sn : qv * c + qp * sn;
+        }
+      }
+      sk[idx] = kv * a.k_scale;
+      sq[idx] = qv;
+    }
+    for (int idx = threadIdx.x; idx < nb * vdim; idx += RET_THREADS) {
+      const int t = idx / vdim, c = idx - t * vdim;
+      const float* row = a.rows + (long long)(n0 + t) * a.row_width;
+      float v = row[a.v_col + h * vdim + c];
+      for (int s = 1; s < a.n_partials; ++s) v += row[s * a.partial_stride + a.v_col + h * vdim + c];
+      sv[idx] = v;
+      if (MODE != 1) {
+        float g = row[a.g_col + h * vdim + c];
+        for (int s = 1; s < a.n_partials; ++s) g += row[s * a.partial_stride + a.g_col + h * vdim + c];
+        sg[idx] = g;
+      }
+    }
+    __syncthreads();
+    if (active) {
+      for (int t = 0; t < nb; ++t) {
+        const float vj = sv[t * vdim + j];
+        const float* kt = sk + t * dim;
+        const float* qt = sq + t * dim;
+        float o = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int i = sl + r * slices;
+          if (i < dim) {
+            const float sn = fmaf(decay, S[r], kt[i] * vj);
+            S[r] = sn;
+            o = fmaf(sn, qt[i], o);
+          }
+        }
+        if (MODE != 1) po[(t * slices + sl) * vdim + j] = o;
+      }
+    }
+    if (MODE != 1) {
+      __syncthreads();
+      for (int t = warp; t < nb; t += RET_THREADS / 32) {
+        float ss = 0.f;
+        for (int c = lane; c < vdim; c += 32) {
+          float o = po[t * slices * vdim + c];
+          for (int s = 1; s < slices; ++s) o += po[(t * slices + s) * vdim + c];
+          po[t * slices * vdim + c] = o;
+          ss = fmaf(o, o, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)vdim + a.eps);
+        for (int c = lane; c < vdim; c += 32) {
+          const float g = sg[t * vdim + c];
+          out[((long long)(n0 + t) * a.nh + h) * vdim + c] = from_f32<OT>(po[t * slices * vdim + c] * inv * (g / (1.0f + expf(-g))));
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (MODE != 2 && active) {
+    float* dst = MODE == 0 ? gstate : cr;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = sl + r * slices;
+      if (i < dim) dst[i * vdim + j] = S[r];
+    }
+  }
+}
+
 // Walks a sequence's pieces: piece p starts from what the pieces before it make of the sequence's state.
 __global__ void __launch_bounds__(256) retention_join_kernel(RetentionArgs a) {
   pdl_launch_dependents();
@@ -426,27 +557,61 @@ __global__ void __launch_bounds__(256) retention_join_kernel(RetentionArgs a) {
   *st = S;
 }
 
+template <typename K>
+int retention_attr(K kernel, size_t smem) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llg_fail("retention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  }
+  return 0;
+}
+
+// KERNEL(MODE): the kernel of a mode, whichever form.
+#define RET_RUN(KERNEL, SMEM)                                                                                   \
+  do {                                                                                                          \
+    if (!a.carry) {                                                                                             \
+      if (retention_attr(KERNEL(0), SMEM)) return 1;                                                            \
+      llg_launch(KERNEL(0), dim3(a.nh, 1, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                       \
+      return llg_check_launch("retention");                                                                     \
+    }                                                                                                           \
+    if (retention_attr(KERNEL(1), SMEM) || retention_attr(KERNEL(2), SMEM)) return 1;                           \
+    llg_launch(KERNEL(1), dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                  \
+    llg_launch(retention_join_kernel, dim3((nst + 255) / 256, a.nh, a.n_seqs), dim3(256), 0, stream, a);        \
+    llg_launch(KERNEL(2), dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                  \
+    return llg_check_launch("retention (pieces)");                                                              \
+  } while (0)
+
 template <typename OT>
 int retention_launch(const RetentionArgs& a, size_t smem, cudaStream_t stream) {
-#define RET_ATTR(K)                                                                                             \
-  if (smem > 48 * 1024) {                                                                                       \
-    cudaError_t e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-    if (e != cudaSuccess) return llg_fail("retention: shared memory %zu: %s", smem, cudaGetErrorString(e));     \
-  }
-  if (!a.carry) {
-    RET_ATTR((retention_kernel<OT, 0>));
-    llg_launch(retention_kernel<OT, 0>, dim3(a.nh, 1, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
-    return llg_check_launch("retention");
-  }
-  RET_ATTR((retention_kernel<OT, 1>));
-  RET_ATTR((retention_kernel<OT, 2>));
-#undef RET_ATTR
   const int nst = a.dim * a.vdim;
-  llg_launch(retention_kernel<OT, 1>, dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
-  llg_launch(retention_join_kernel, dim3((nst + 255) / 256, a.nh, a.n_seqs), dim3(256), 0, stream, a);
-  llg_launch(retention_kernel<OT, 2>, dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), smem, stream, a);
-  return llg_check_launch("retention (pieces)");
+  // the state in registers where a thread's share of it is at most 64 elements of one column
+  if (a.vdim <= RET_THREADS) {
+    const int slices = RET_THREADS / a.vdim;
+    const int rows = (a.dim + slices - 1) / slices;
+    const size_t reg_smem = (size_t)RET_BATCH * (2 * a.dim + 2 * a.vdim + slices * a.vdim) * sizeof(float);
+    if (rows <= 64 && reg_smem <= 200 * 1024) {
+#define K4(M) retention_reg_kernel<OT, M, 4>
+#define K8(M) retention_reg_kernel<OT, M, 8>
+#define K16(M) retention_reg_kernel<OT, M, 16>
+#define K32(M) retention_reg_kernel<OT, M, 32>
+#define K64(M) retention_reg_kernel<OT, M, 64>
+      if (rows <= 4) RET_RUN(K4, reg_smem);
+      else if (rows <= 8) RET_RUN(K8, reg_smem);
+      else if (rows <= 16) RET_RUN(K16, reg_smem);
+      else if (rows <= 32) RET_RUN(K32, reg_smem);
+      else RET_RUN(K64, reg_smem);
+#undef K4
+#undef K8
+#undef K16
+#undef K32
+#undef K64
+    }
+  }
+#define KS(M) retention_kernel<OT, M>
+  RET_RUN(KS, smem);
+#undef KS
 }
+#undef RET_RUN
 
 }  // namespace
 
