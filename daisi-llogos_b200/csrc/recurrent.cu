@@ -402,24 +402,26 @@ __global__ void __launch_bounds__(RET_THREADS) retention_kernel(RetentionArgs a)
 
 // The same walk with the state in registers and the tokens taken RET_BATCH at a time: the batch's q, k (rotated), v and
 // gate arguments are summed into shared memory together, so that no token waits for memory on its own; a thread owns
-// column j of the state's rows sl, sl + slices, ... (R of them at most), so the walk through a batch needs no barrier;
-// every token's partial read-outs (one per slice) are left in shared memory and the batch's unit norms and gates are
-// done together, a warp per token.  For value heads of up to RET_THREADS elements and R rows a thread.
+// column j of R neighbouring rows of the state (rows sl * R ...; q and k rows in shared memory are filled with zeros up
+// to slices * R elements, so the walk needs no bounds and reads four elements an access), and the walk through a batch
+// needs no barrier; every token's partial read-outs (one per slice) are left in shared memory and the batch's unit
+// norms and gates are done together, a warp per token.  For value heads of up to THREADS elements.
 constexpr int RET_BATCH = 16;
 
-template <typename OT, int MODE, int R>
-__global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArgs a) {
+template <typename OT, int MODE, int R, int THREADS>
+__global__ void __launch_bounds__(THREADS) retention_reg_kernel(RetentionArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
   const int h = blockIdx.x, piece = blockIdx.y, b = blockIdx.z;
   const int dim = a.dim, vdim = a.vdim, nst = dim * vdim;
-  const int slices = RET_THREADS / vdim;
+  const int slices = THREADS / vdim;
+  const int dp = slices * R;                 // padded length of a q or k row (a multiple of four, at least dim)
   const bool active = threadIdx.x < slices * vdim;
   const int sl = threadIdx.x / vdim, j = threadIdx.x - sl * vdim;
-  float* sq = smem;                          // [RET_BATCH][dim]
-  float* sk = sq + RET_BATCH * dim;          // [RET_BATCH][dim]
-  float* sv = sk + RET_BATCH * dim;          // [RET_BATCH][vdim]
+  float* sq = smem;                          // [RET_BATCH][dp]
+  float* sk = sq + RET_BATCH * dp;           // [RET_BATCH][dp]
+  float* sv = sk + RET_BATCH * dp;           // [RET_BATCH][vdim]
   float* sg = sv + RET_BATCH * vdim;         // [RET_BATCH][vdim]
   float* po = sg + RET_BATCH * vdim;         // [RET_BATCH][slices][vdim]
   const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
@@ -435,7 +437,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArg
   float S[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = sl + r * slices;
+    const int i = sl * R + r;
     S[r] = (active && i < dim && MODE != 1) ? (MODE == 0 ? gstate : cr)[i * vdim + j] : 0.f;
   }
   const float decay = a.decay[h];
@@ -444,33 +446,36 @@ __global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArg
   OT* out = (OT*)a.out;
   for (int n0 = lo; n0 < hi; n0 += RET_BATCH) {
     const int nb = hi - n0 < RET_BATCH ? hi - n0 : RET_BATCH;
-    for (int idx = threadIdx.x; idx < nb * dim; idx += RET_THREADS) {
-      const int t = idx / dim, i = idx - t * dim;
-      const float* row = a.rows + (long long)(n0 + t) * a.row_width;
-      auto summed = [&](int col) {
-        float v = row[col];
-        for (int s = 1; s < a.n_partials; ++s) v += row[s * a.partial_stride + col];
-        return v;
-      };
-      float kv = summed(a.k_col + h * dim + i);
-      float qv = MODE != 1 ? summed(a.q_col + h * dim + i) : 0.f;
-      if (i < rd) {
-        int pos = a.positions[n0 + t];
-        if (pos >= a.table_positions) pos = a.table_positions - 1;
-        const int f = i < half ? i : i - half;
-        const int ip = i < half ? i + half : i - half;
-        const float c = a.cos_table[(long long)pos * half + f], sn = a.sin_table[(long long)pos * half + f];
-        const float kp = summed(a.k_col + h * dim + ip);
-        kv = i < half ? kv * c - kp * sn : kv * c + kp * sn;
-        if (MODE != 1) {
-          const float qp = summed(a.q_col + h * dim + ip);
-          qv = i < half ? qv * c - qp * sn : qv * c + qp * sn;
+    for (int idx = threadIdx.x; idx < nb * dp; idx += THREADS) {
+      const int t = idx / dp, i = idx - t * dp;
+      float kv = 0.f, qv = 0.f;
+      if (i < dim) {
+        const float* row = a.rows + (long long)(n0 + t) * a.row_width;
+        auto summed = [&](int col) {
+          float v = row[col];
+          for (int s = 1; s < a.n_partials; ++s) v += row[s * a.partial_stride + col];
+          return v;
+        };
+        kv = summed(a.k_col + h * dim + i);
+        if (MODE != 1) qv = summed(a.q_col + h * dim + i);
+        if (i < rd) {
+          int pos = a.positions[n0 + t];
+          if (pos >= a.table_positions) pos = a.table_positions - 1;
+          const int f = i < half ? i : i - half;
+          const int ip = i < half ? i + half : i - half;
+          const float c = a.cos_table[(long long)pos * half + f], sn = a.sin_table[(long long)pos * half + f];
+          const float kp = summed(a.k_col + h * dim + ip);
+          kv = i < half ? kv * c - kp * sn : kv * c + kp * sn;
+          if (MODE != 1) {
+            const float qp = summed(a.q_col + h * dim + ip);
+            qv = i < half ? qv * c - qp * sn : qv * c + qp * sn;
+          }
         }
       }
       sk[idx] = kv * a.k_scale;
       sq[idx] = qv;
     }
-    for (int idx = threadIdx.x; idx < nb * vdim; idx += RET_THREADS) {
+    for (int idx = threadIdx.x; idx < nb * vdim; idx += THREADS) {
       const int t = idx / vdim, c = idx - t * vdim;
       const float* row = a.rows + (long long)(n0 + t) * a.row_width;
       float v = row[a.v_col + h * vdim + c];
@@ -486,16 +491,24 @@ __global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArg
     if (active) {
       for (int t = 0; t < nb; ++t) {
         const float vj = sv[t * vdim + j];
-        const float* kt = sk + t * dim;
-        const float* qt = sq + t * dim;
+        const float4* kt = reinterpret_cast<const float4*>(sk + t * dp + sl * R);
+        const float4* qt = reinterpret_cast<const float4*>(sq + t * dp + sl * R);
         float o = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const int i = sl + r * slices;
-          if (i < dim) {
-            const float sn = fmaf(decay, S[r], kt[i] * vj);
-            S[r] = sn;
-            o = fmaf(sn, qt[i], o);
+        for (int r4 = 0; r4 < R / 4; ++r4) {
+          const float4 kk = kt[r4];
+          float sn;
+          if (MODE != 1) {
+            const float4 qq = qt[r4];
+            sn = fmaf(decay, S[4 * r4], kk.x * vj); S[4 * r4] = sn; o = fmaf(sn, qq.x, o);
+            sn = fmaf(decay, S[4 * r4 + 1], kk.y * vj); S[4 * r4 + 1] = sn; o = fmaf(sn, qq.y, o);
+            sn = fmaf(decay, S[4 * r4 + 2], kk.z * vj); S[4 * r4 + 2] = sn; o = fmaf(sn, qq.z, o);
+            sn = fmaf(decay, S[4 * r4 + 3], kk.w * vj); S[4 * r4 + 3] = sn; o = fmaf(sn, qq.w, o);
+          } else {
+            S[4 * r4] = fmaf(decay, S[4 * r4], kk.x * vj);
+            S[4 * r4 + 1] = fmaf(decay, S[4 * r4 + 1], kk.y * vj);
+            S[4 * r4 + 2] = fmaf(decay, S[4 * r4 + 2], kk.z * vj);
+            S[4 * r4 + 3] = fmaf(decay, S[4 * r4 + 3], kk.w * vj);
           }
         }
         if (MODE != 1) po[(t * slices + sl) * vdim + j] = o;
@@ -503,7 +516,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArg
     }
     if (MODE != 1) {
       __syncthreads();
-      for (int t = warp; t < nb; t += RET_THREADS / 32) {
+      for (int t = warp; t < nb; t += THREADS / 32) {
         float ss = 0.f;
         for (int c = lane; c < vdim; c += 32) {
           float o = po[t * slices * vdim + c];
@@ -525,13 +538,14 @@ __global__ void __launch_bounds__(RET_THREADS) retention_reg_kernel(RetentionArg
     float* dst = MODE == 0 ? gstate : cr;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const int i = sl + r * slices;
+      const int i = sl * R + r;
       if (i < dim) dst[i * vdim + j] = S[r];
     }
   }
 }
 
-// Walks a sequence's pieces: piece p starts from what the pieces before it make of the sequence's state.
+// Walks a sequence's pieces: piece p starts from what the pieces before it make of the sequence's state.  The states the
+// pieces reached are fetched SCAN_BATCH at a time, ahead of the chain of multiplications.
 __global__ void __launch_bounds__(256) retention_join_kernel(RetentionArgs a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -543,16 +557,32 @@ __global__ void __launch_bounds__(256) retention_join_kernel(RetentionArgs a) {
   const int t_begin = a.cu_tokens[b], t_end = a.cu_tokens[b + 1];
   float* st = a.state + ((long long)a.slots[b] * a.nh + h) * nst + e;
   float S = *st;
-  for (int p = 0; p < a.pieces; ++p) {
-    int lo = t_begin + p * LLG_RETENTION_PIECE;
-    if (lo > t_end) lo = t_end;
-    const int hi = (p == a.pieces - 1 || lo + LLG_RETENTION_PIECE > t_end) ? t_end : lo + LLG_RETENTION_PIECE;
-    float* cr = a.carry + (((long long)b * a.pieces + p) * a.nh + h) * nst + e;
-    const float reached = *cr;
-    *cr = S;
-    float A = 1.f;
-    for (int t = lo; t < hi; ++t) A *= decay;
-    S = A * S + reached;
+  // decay^LLG_RETENTION_PIECE by the same chain of roundings as a walk through a whole piece
+  float whole = 1.f;
+  for (int t = 0; t < LLG_RETENTION_PIECE; ++t) whole *= decay;
+  const long long step = (long long)a.nh * nst;
+  float* cr = a.carry + (((long long)b * a.pieces) * a.nh + h) * nst + e;
+  for (int p0 = 0; p0 < a.pieces; p0 += SCAN_BATCH, cr += SCAN_BATCH * step) {
+    float reached[SCAN_BATCH];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k)
+      if (p0 + k < a.pieces) reached[k] = cr[k * step];
+#pragma unroll
+    for (int k = 0; k < SCAN_BATCH; ++k) {
+      const int p = p0 + k;
+      if (p < a.pieces) {
+        int lo = t_begin + p * LLG_RETENTION_PIECE;
+        if (lo > t_end) lo = t_end;
+        const int hi = (p == a.pieces - 1 || lo + LLG_RETENTION_PIECE > t_end) ? t_end : lo + LLG_RETENTION_PIECE;
+        float A = whole;
+        if (hi - lo != LLG_RETENTION_PIECE) {
+          A = 1.f;
+          for (int t = lo; t < hi; ++t) A *= decay;
+        }
+        cr[k * step] = S;
+        S = A * S + reached[k];
+      }
+    }
   }
   *st = S;
 }
@@ -567,48 +597,65 @@ int retention_attr(K kernel, size_t smem) {
 }
 
 // KERNEL(MODE): the kernel of a mode, whichever form.
-#define RET_RUN(KERNEL, SMEM)                                                                                   \
+#define RET_RUN(KERNEL, SMEM, THREADS)                                                                                 \
   do {                                                                                                          \
     if (!a.carry) {                                                                                             \
       if (retention_attr(KERNEL(0), SMEM)) return 1;                                                            \
-      llg_launch(KERNEL(0), dim3(a.nh, 1, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                       \
+      llg_launch(KERNEL(0), dim3(a.nh, 1, a.n_seqs), dim3(THREADS), SMEM, stream, a);                           \
       return llg_check_launch("retention");                                                                     \
     }                                                                                                           \
     if (retention_attr(KERNEL(1), SMEM) || retention_attr(KERNEL(2), SMEM)) return 1;                           \
-    llg_launch(KERNEL(1), dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                  \
+    llg_launch(KERNEL(1), dim3(a.nh, a.pieces, a.n_seqs), dim3(THREADS), SMEM, stream, a);                      \
     llg_launch(retention_join_kernel, dim3((nst + 255) / 256, a.nh, a.n_seqs), dim3(256), 0, stream, a);        \
-    llg_launch(KERNEL(2), dim3(a.nh, a.pieces, a.n_seqs), dim3(RET_THREADS), SMEM, stream, a);                  \
+    llg_launch(KERNEL(2), dim3(a.nh, a.pieces, a.n_seqs), dim3(THREADS), SMEM, stream, a);                      \
     return llg_check_launch("retention (pieces)");                                                              \
   } while (0)
 
 template <typename OT>
 int retention_launch(const RetentionArgs& a, size_t smem, cudaStream_t stream) {
   const int nst = a.dim * a.vdim;
-  // the state in registers where a thread's share of it is at most 64 elements of one column
-  if (a.vdim <= RET_THREADS) {
-    const int slices = RET_THREADS / a.vdim;
+  // The state in registers where a thread's share of it is at most 32 rows of one column: with 256 threads, or with
+  // 512 where that halves a share of more than 32 rows.
+  for (int threads = RET_THREADS; threads <= 2 * RET_THREADS; threads *= 2) {
+    if (a.vdim > threads) continue;
+    const int slices = threads / a.vdim;
     const int rows = (a.dim + slices - 1) / slices;
-    const size_t reg_smem = (size_t)RET_BATCH * (2 * a.dim + 2 * a.vdim + slices * a.vdim) * sizeof(float);
-    if (rows <= 64 && reg_smem <= 200 * 1024) {
-#define K4(M) retention_reg_kernel<OT, M, 4>
-#define K8(M) retention_reg_kernel<OT, M, 8>
-#define K16(M) retention_reg_kernel<OT, M, 16>
-#define K32(M) retention_reg_kernel<OT, M, 32>
-#define K64(M) retention_reg_kernel<OT, M, 64>
-      if (rows <= 4) RET_RUN(K4, reg_smem);
-      else if (rows <= 8) RET_RUN(K8, reg_smem);
-      else if (rows <= 16) RET_RUN(K16, reg_smem);
-      else if (rows <= 32) RET_RUN(K32, reg_smem);
-      else RET_RUN(K64, reg_smem);
+    if (rows > 32) continue;
+    const int r = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+    const size_t reg_smem = (size_t)RET_BATCH * (2 * slices * r + 2 * a.vdim + slices * a.vdim) * sizeof(float);
+    if (reg_smem > 200 * 1024) continue;
+#define RET_THREADS_ARG(T) T
+#define K4(M) retention_reg_kernel<OT, M, 4, 256>
+#define K8(M) retention_reg_kernel<OT, M, 8, 256>
+#define K16(M) retention_reg_kernel<OT, M, 16, 256>
+#define K32(M) retention_reg_kernel<OT, M, 32, 256>
+#define K4W(M) retention_reg_kernel<OT, M, 4, 512>
+#define K8W(M) retention_reg_kernel<OT, M, 8, 512>
+#define K16W(M) retention_reg_kernel<OT, M, 16, 512>
+#define K32W(M) retention_reg_kernel<OT, M, 32, 512>
+    if (threads == RET_THREADS) {
+      if (r == 4) RET_RUN(K4, reg_smem, 256);
+      else if (r == 8) RET_RUN(K8, reg_smem, 256);
+      else if (r == 16) RET_RUN(K16, reg_smem, 256);
+      else RET_RUN(K32, reg_smem, 256);
+    } else {
+      if (r == 4) RET_RUN(K4W, reg_smem, 512);
+      else if (r == 8) RET_RUN(K8W, reg_smem, 512);
+      else if (r == 16) RET_RUN(K16W, reg_smem, 512);
+      else RET_RUN(K32W, reg_smem, 512);
+    }
 #undef K4
 #undef K8
 #undef K16
 #undef K32
-#undef K64
-    }
+#undef K4W
+#undef K8W
+#undef K16W
+#undef K32W
+#undef RET_THREADS_ARG
   }
 #define KS(M) retention_kernel<OT, M>
-  RET_RUN(KS, smem);
+  RET_RUN(KS, smem, RET_THREADS);
 #undef KS
 }
 #undef RET_RUN
