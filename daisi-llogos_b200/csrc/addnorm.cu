@@ -20,7 +20,31 @@ LLG_API int llg_addnorm_max_outs() { return LLG_ADDNORM_OUTS; }
 
 namespace {
 
-template <typename OT>
+template <int VEC> struct Pack { float v[VEC]; };
+
+template <int VEC> __device__ __forceinline__ Pack<VEC> load_f32(const float* p) {
+  Pack<VEC> r;
+  if (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[VEC > 1 ? 1 : 0] = t.y; r.v[VEC > 2 ? 2 : 0] = t.z; r.v[VEC > 3 ? 3 : 0] = t.w; }
+  else r.v[0] = *p;
+  return r;
+}
+template <int VEC> __device__ __forceinline__ void store(float* p, const Pack<VEC>& r) {
+  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[VEC > 1 ? 1 : 0], r.v[VEC > 2 ? 2 : 0], r.v[VEC > 3 ? 3 : 0]);
+  else *p = r.v[0];
+}
+template <int VEC> __device__ __forceinline__ void store(__nv_bfloat16* p, const Pack<VEC>& r) {
+  if (VEC == 4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[VEC > 1 ? 1 : 0]), hi = __floats2bfloat162_rn(r.v[VEC > 2 ? 2 : 0], r.v[VEC > 3 ? 3 : 0]);
+    uint2 t;
+    t.x = *reinterpret_cast<const unsigned int*>(&lo);
+    t.y = *reinterpret_cast<const unsigned int*>(&hi);
+    *reinterpret_cast<uint2*>(p) = t;
+  } else *p = __float2bfloat16_rn(r.v[0]);
+}
+
+// VEC 4: every access moves four neighbouring elements (the host has checked sizes and addresses).  A term's partial sums
+// are fetched four sets at a time, so that the few rows of a decode step do not wait for one load after another.
+template <typename OT, int VEC>
 __global__ void __launch_bounds__(1024) multi_add_rmsnorm_kernel(AddNormArgs a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -32,42 +56,76 @@ __global__ void __launch_bounds__(1024) multi_add_rmsnorm_kernel(AddNormArgs a) 
   const int j = blockIdx.x;
   const int r = a.rows ? a.rows[j] : j;
   float* res = a.residual + (long long)r * hidden;
+  const int first = threadIdx.x * VEC, stride = blockDim.x * VEC;
   // every thread owns the same elements of the row in every pass, so the passes need no barrier of their own
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = res[i];
+  for (int i = first; i < hidden; i += stride) store<VEC>(row + i, load_f32<VEC>(res + i));
   for (int t = 0; t < a.n_terms; ++t) {
     const AddNormTerm& term = a.terms[t];
     const float* p = term.data + (long long)r * hidden;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-      float y = p[i];
-      for (int s = 1; s < term.n_partials; ++s) y += p[s * a.partial_stride + i];
-      tmp[i] = y;
-      ss = fmaf(y, y, ss);
+    for (int i = first; i < hidden; i += stride) {
+      Pack<VEC> y = load_f32<VEC>(p + i);
+      int s = 1;
+      for (; s + 3 < term.n_partials; s += 4) {
+        const Pack<VEC> y0 = load_f32<VEC>(p + s * a.partial_stride + i), y1 = load_f32<VEC>(p + (s + 1) * a.partial_stride + i);
+        const Pack<VEC> y2 = load_f32<VEC>(p + (s + 2) * a.partial_stride + i), y3 = load_f32<VEC>(p + (s + 3) * a.partial_stride + i);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) y.v[c] = (((y.v[c] + y0.v[c]) + y1.v[c]) + y2.v[c]) + y3.v[c];
+      }
+      for (; s < term.n_partials; ++s) {
+        const Pack<VEC> y0 = load_f32<VEC>(p + s * a.partial_stride + i);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) y.v[c] += y0.v[c];
+      }
+      if (term.norm_w) {
+        store<VEC>(tmp + i, y);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) ss = fmaf(y.v[c], y.v[c], ss);
+      } else {
+        Pack<VEC> v = load_f32<VEC>(row + i);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) v.v[c] += term.scale * y.v[c];
+        store<VEC>(row + i, v);
+      }
     }
     if (term.norm_w) {
       ss = block_sum(ss, part);
       const float inv = 1.0f / sqrtf(ss / (float)hidden + term.norm_eps);
-      for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] += term.scale * (tmp[i] * inv * term.norm_w[i]);
-    } else {
-      for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] += term.scale * tmp[i];
+      for (int i = first; i < hidden; i += stride) {
+        Pack<VEC> v = load_f32<VEC>(row + i);
+        const Pack<VEC> y = load_f32<VEC>(tmp + i), w = load_f32<VEC>(term.norm_w + i);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) v.v[c] += term.scale * (y.v[c] * inv * w.v[c]);
+        store<VEC>(row + i, v);
+      }
     }
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = row[i];
-    if (a.n_terms) res[i] = v;
-    ss = fmaf(v, v, ss);
+  for (int i = first; i < hidden; i += stride) {
+    const Pack<VEC> v = load_f32<VEC>(row + i);
+    if (a.n_terms) store<VEC>(res + i, v);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) ss = fmaf(v.v[c], v.v[c], ss);
   }
-  ss = block_sum(ss, part);
-  const float inv = 1.0f / sqrtf(ss / (float)hidden + a.eps);
+  bool normed = false;
+  for (int o = 0; o < a.n_outs; ++o) normed = normed || a.outs[o].weight != nullptr;
+  float inv = 1.f;
+  if (normed) {
+    ss = block_sum(ss, part);
+    inv = 1.0f / sqrtf(ss / (float)hidden + a.eps);
+  }
   for (int o = 0; o < a.n_outs; ++o) {
     OT* out = (OT*)a.outs[o].out + (long long)j * hidden;
     const float* w = a.outs[o].weight;
     const float off = a.outs[o].offset;
-    if (w) {
-      for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = from_f32<OT>(row[i] * inv * (off + w[i]));
-    } else {
-      for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = from_f32<OT>(row[i]);
+    for (int i = first; i < hidden; i += stride) {
+      Pack<VEC> v = load_f32<VEC>(row + i);
+      if (w) {
+        const Pack<VEC> ww = load_f32<VEC>(w + i);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) v.v[c] = v.v[c] * inv * (off + ww.v[c]);
+      }
+      store<VEC>(out + i, v);
     }
   }
 }
@@ -162,20 +220,32 @@ LLG_API int llg_multi_add_rmsnorm(const AddNormArgs* args, cudaStream_t stream) 
   if (a.n_out == 0) return 0;
   const size_t smem = 2 * (size_t)a.hidden * sizeof(float);
   LLG_REQUIRE(smem <= 200 * 1024, "multi_add_rmsnorm: rows of %d elements do not fit shared memory", a.hidden);
-  const int threads = threads_for(a.hidden);
-#define LAUNCH(OT)                                                                                                \
+  auto aligned = [](const void* p) { return ((size_t)p % 16) == 0; };
+  bool vec = a.hidden % 4 == 0 && a.partial_stride % 4 == 0 && aligned(a.residual);
+  for (int t = 0; t < a.n_terms; ++t) vec = vec && aligned(a.terms[t].data) && aligned(a.terms[t].norm_w);
+  for (int o = 0; o < a.n_outs; ++o) vec = vec && aligned(a.outs[o].out) && aligned(a.outs[o].weight);
+  int threads = vec ? threads_for(a.hidden) : threads_for(4 * a.hidden);
+  // many rows: smaller blocks, so that a multiprocessor holds several rows at different stages
+  if (a.n_out > 2 * llg_sm_count() && threads > 256) threads = 256;
+#define LAUNCH_V(OT, V)                                                                                           \
   do {                                                                                                            \
-    auto k = multi_add_rmsnorm_kernel<OT>;                                                                        \
+    auto k = multi_add_rmsnorm_kernel<OT, V>;                                                                     \
     if (smem > 48 * 1024) {                                                                                       \
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
       if (e != cudaSuccess) return llg_fail("multi_add_rmsnorm: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
     }                                                                                                             \
     llg_launch(k, dim3(a.n_out), dim3(threads), smem, stream, a);                                                 \
   } while (0)
+#define LAUNCH(OT)            \
+  do {                        \
+    if (vec) LAUNCH_V(OT, 4); \
+    else LAUNCH_V(OT, 1);     \
+  } while (0)
   if (a.out_dtype == LLG_F32) LAUNCH(float);
   else if (a.out_dtype == LLG_BF16) LAUNCH(__nv_bfloat16);
   else return llg_fail("multi_add_rmsnorm: unknown output type %d", a.out_dtype);
 #undef LAUNCH
+#undef LAUNCH_V
   return llg_check_launch("multi_add_rmsnorm");
 }
 

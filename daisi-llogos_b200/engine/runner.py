@@ -161,7 +161,7 @@ class BlockRunner:
             n1, mx, n2, ff = (block.parts[r] for r in ("norm1", "mixer", "norm2", "ffn"))
             if type(n1) is not RmsNorm or type(n2) is not RmsNorm or type(mx) is not Attention or type(ff) is not SwiGLU:
                 return None
-            if mx.special or mx.blend_group is not None or ff.activation != "silu":
+            if mx.special or mx.blend_group is not None or ff.activation != "silu" or n1.weight_offset or n2.weight_offset:
                 return None                                   # forms of attention and gating the native chain does not launch
             if not mx.own_kv or n1.size != mx.hidden or n2.size != mx.hidden or ff.hidden != mx.hidden:
                 return None

@@ -1055,6 +1055,16 @@ CONV_MAX_TAPS = 16           # taps of a short convolution; checked against the 
 RETENTION_PIECE = 128        # tokens of a piece of retention's walk; checked against the library at first use
 
 
+def retention_supported(dim: int, vdim: int) -> bool:
+    """Whether ``retention`` takes heads of these sizes (the rule of csrc/recurrent.cu: the state of a head lies in the
+    registers of 256 or 512 threads, at most 32 rows of one column each, or else whole in shared memory)."""
+    for threads in (256, 512):
+        if vdim <= threads and -(-dim // (threads // vdim)) <= 32:
+            return True
+    slices = max(1, 256 // vdim)
+    return (dim * vdim + 2 * dim + 2 * vdim + slices * vdim) * 4 <= 220 * 1024
+
+
 def causal_conv(rows: torch.Tensor, col0: int, weight: torch.Tensor, state: Optional[torch.Tensor], slots: torch.Tensor,
                 cu_tokens: torch.Tensor, seq_of_token: torch.Tensor, len_before: torch.Tensor, out: torch.Tensor,
                 in_bias: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,

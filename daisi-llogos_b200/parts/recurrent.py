@@ -11,6 +11,11 @@ along every sequence of the step from the state the cache holds (float32 ``[slot
 sequence starts), leaves the last state there and writes ``S_t * silu(g_t)`` in the compute type for the output
 product.  Because the recurrence is linear in S, a step's tokens are scanned in pieces that are joined afterwards, so a
 prompt does not run token by token; gates, candidates and the state are float32 whatever the compute type.
+
+``RgLru`` (a block around a real-gated linear recurrent unit, with a short convolution ahead of it), ``Retention`` (a
+matrix-valued state per head under a fixed decay, read out by the query) and ``SideBySide`` (two mixers over the same
+input, each normed and the two weighed) follow the same pattern: one input product, float32 kernels for what enters the
+recurrence, a state per sequence in the cache (several things per sequence are a ``MultiNeed``), pieces for long prompts.
 """
 from __future__ import annotations
 
@@ -165,6 +170,10 @@ class Retention(Mixer):
         if len(self.decay) != self.nh:
             raise ValueError(f"retention: {len(self.decay)} decays for {self.nh} heads")
         self.eps = float(p["norm_eps"])
+        fits = getattr(env.ops, "retention_supported", None)
+        if fits is not None and not fits(self.hd, self.vd):
+            raise ValueError(f"retention: a head's state of {self.hd} x {self.vd} elements fits neither the registers nor "
+                             f"the shared memory of one block")
         self.k_scale = float(self.hd) ** -0.5
         enc = p.get("position")
         self.encoding = env.encodings[enc] if enc is not None else None
