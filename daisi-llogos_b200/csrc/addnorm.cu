@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(1024) hash_embed_kernel(HashEmbedArgs a) {
       }
       if (prev < 0 || prev >= a.vocab) prev = 0;
       if (!has_prev) pr = a.buckets;
-      else pr = (int)(((long long)prev * a.mul_prev + (long long)tok * a.mul_cur) % (long long)a.buckets);
+      else pr = (int)((((long long)prev * (a.mul_prev % a.buckets)) % a.buckets + ((long long)tok * (a.mul_cur % a.buckets)) % a.buckets) % a.buckets);
       if (pr < 0) pr += a.buckets;
     }
     pair_row = pr;

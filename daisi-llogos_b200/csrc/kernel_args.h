@@ -406,7 +406,8 @@ struct HashEmbedArgs {
   float scale;
   const void* pair_table;     // [buckets + 1][hidden] or null
   int pair_dtype;
-  int buckets, mul_prev, mul_cur;
+  int buckets;
+  long long mul_prev, mul_cur;
   const int* token_ids;       // [n_tokens]
   const int* positions;       // [n_tokens]
   const int* seq_of_token;    // [n_tokens]

@@ -235,7 +235,7 @@ class _AddNormArgs(Structure):
 class _HashEmbedArgs(Structure):
     _fields_ = [
         ("table", c_void_p), ("table_dtype", c_int), ("scale", c_float), ("pair_table", c_void_p), ("pair_dtype", c_int),
-        ("buckets", c_int), ("mul_prev", c_int), ("mul_cur", c_int),
+        ("buckets", c_int), ("mul_prev", c_longlong), ("mul_cur", c_longlong),
         ("token_ids", c_void_p), ("positions", c_void_p), ("seq_of_token", c_void_p), ("cu_tokens", c_void_p),
         ("slots", c_void_p), ("last_token", c_void_p), ("norm_w", c_void_p), ("norm_offset", c_float), ("eps", c_float),
         ("out", c_void_p), ("n_tokens", c_int), ("vocab", c_int), ("hidden", c_int),
