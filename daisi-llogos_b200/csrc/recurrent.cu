@@ -208,6 +208,96 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(ConvArgs a) {
   for (int s = 0; s < K - 1; ++s) st[(long long)s * a.channels] = fresh[s];
 }
 
+// The same for a number of taps known when the kernel is compiled (2 to 4): a thread walks CONV_RUN neighbouring tokens of
+// one channel and keeps the inputs it has fetched as the next tokens' window, so an input is read about once instead of
+// once per tap, and the taps' weights once per run.  A sequence's first step tokens (the ones whose taps reach before the
+// step) are still all done by the thread that meets the sequence's first token, state first, new state last.
+constexpr int CONV_RUN = 8;
+
+template <typename O2, int K>
+__global__ void __launch_bounds__(128) causal_conv_run_kernel(ConvArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n_first = blockIdx.x * CONV_RUN;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const float ib = a.in_bias ? a.in_bias[c] : 0.f, ob = a.bias ? a.bias[c] : 0.f;
+  float w[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) w[j] = a.weight[(long long)c * K + j];
+  auto fetch = [&](int token) {                    // the input at packed token `token`
+    const float* r = a.rows + (long long)token * a.row_width + a.col0 + c;
+    float v = r[0];
+    for (int s = 1; s < a.n_partials; ++s) v += r[s * a.partial_stride];
+    return v + ib;
+  };
+  O2* out2 = (O2*)a.out2;
+  float win[K - 1];                                // win[d - 1]: the input of the token d before the current one
+  int have = 0;                                    // how many of them are held
+  const int n_last = n_first + CONV_RUN < a.n_tokens ? n_first + CONV_RUN : a.n_tokens;
+  for (int n = n_first; n < n_last; ++n) {
+    const int b = a.seq_of_token[n];
+    const int t0 = a.cu_tokens[b];
+    const int p = n - t0;
+    if (p < K - 1) {
+      have = 0;                                    // the window does not reach across a sequence's start
+      if (p > 0) continue;                         // done with the sequence's first step token
+      const int count = a.cu_tokens[b + 1] - t0;
+      float vals[2 * K];
+      float* st = a.state + (long long)a.slots[b] * (K - 1) * a.channels + c;
+      const int lb = a.len_before[b];
+#pragma unroll
+      for (int s = 0; s < K - 1; ++s) vals[s] = (lb - (K - 1) + s >= 0) ? st[(long long)s * a.channels] : 0.f;
+      const int m = count < K - 1 ? count : K - 1;
+#pragma unroll
+      for (int q = 0; q < K - 1; ++q) vals[K - 1 + q] = q < m ? fetch(t0 + q) : 0.f;
+#pragma unroll
+      for (int q = 0; q < K - 1; ++q) {
+        if (q < m) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < K; ++j) acc = fmaf(w[j], vals[q + j], acc);
+          acc += ob;
+          a.out[(long long)(t0 + q) * a.channels + c] = acc;
+          if (out2) out2[(long long)(t0 + q) * a.channels + c] = from_f32<O2>(acc);
+        }
+      }
+      float fresh[K - 1];
+#pragma unroll
+      for (int s = 0; s < K - 1; ++s) {
+        const int q = count - (K - 1) + s;         // the step token whose input becomes state entry s
+        float v;
+        if (q >= m) v = fetch(t0 + q);
+        else {
+          v = 0.f;
+#pragma unroll
+          for (int e = 0; e < 2 * K - 2; ++e)      // vals[s + count] (q < 0) or vals[K - 1 + q], without a runtime index
+            if (e == (q >= 0 ? K - 1 + q : s + count)) v = vals[e];
+        }
+        fresh[s] = v;
+      }
+#pragma unroll
+      for (int s = 0; s < K - 1; ++s) st[(long long)s * a.channels] = fresh[s];
+      continue;
+    }
+    const float x = fetch(n);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+      const int d = K - 1 - j;                     // tap j weighs the token d before
+      const float v = d <= have ? win[d - 1] : fetch(n - d);
+      acc = fmaf(w[j], v, acc);
+    }
+    acc = fmaf(w[K - 1], x, acc) + ob;
+    a.out[(long long)n * a.channels + c] = acc;
+    if (out2) out2[(long long)n * a.channels + c] = from_f32<O2>(acc);
+#pragma unroll
+    for (int d = K - 2; d > 0; --d) win[d] = win[d - 1];
+    win[0] = x;
+    if (have < K - 1) ++have;
+  }
+}
+
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // MODE as in mingru_scan_kernel.
@@ -674,9 +764,24 @@ LLG_API int llg_causal_conv(const ConvArgs* args, cudaStream_t stream) {
   if (a.n_tokens == 0) return 0;
   dim3 grid(a.n_tokens, (a.channels + 127) / 128);
   LLG_REQUIRE(grid.y <= 65535, "causal_conv: too many channels");
-  if (!a.out2 || a.out2_dtype == LLG_F32) llg_launch(causal_conv_kernel<float>, grid, dim3(128), 0, stream, a);
-  else if (a.out2_dtype == LLG_BF16) llg_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
-  else return llg_fail("causal_conv: unknown output type %d", a.out2_dtype);
+  LLG_REQUIRE(!a.out2 || a.out2_dtype == LLG_F32 || a.out2_dtype == LLG_BF16, "causal_conv: unknown output type %d", a.out2_dtype);
+  const bool bf = a.out2 && a.out2_dtype == LLG_BF16;
+  // steps of many tokens and 2 to 4 taps: runs of tokens a thread
+  if (a.taps >= 2 && a.taps <= 4 && a.n_tokens >= 4 * CONV_RUN) {
+    dim3 runs((a.n_tokens + CONV_RUN - 1) / CONV_RUN, grid.y);
+#define CONV_RUN_LAUNCH(K)                                                                               \
+  do {                                                                                                   \
+    if (bf) llg_launch(causal_conv_run_kernel<__nv_bfloat16, K>, runs, dim3(128), 0, stream, a);         \
+    else llg_launch(causal_conv_run_kernel<float, K>, runs, dim3(128), 0, stream, a);                    \
+  } while (0)
+    if (a.taps == 2) CONV_RUN_LAUNCH(2);
+    else if (a.taps == 3) CONV_RUN_LAUNCH(3);
+    else CONV_RUN_LAUNCH(4);
+#undef CONV_RUN_LAUNCH
+    return llg_check_launch("causal_conv (runs)");
+  }
+  if (bf) llg_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
+  else llg_launch(causal_conv_kernel<float>, grid, dim3(128), 0, stream, a);
   return llg_check_launch("causal_conv");
 }
 
