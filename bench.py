@@ -434,7 +434,7 @@ def piratar_config(size):
     layers = [dict(par, mlp=dict(dense)), dict(rec, mlp=dict(moe)), dict(par, mlp=dict(dense)), dict(par, mlp=dict(moe))]
     assert len(layers) == DESIGN_LAYERS
     return {"architecture": "Piratar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"scale": float(width) ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": float(width) ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 1009, "mul_cur": 101}},
             "token_side": {"dim": 64}, "layers": layers}
 
 
