@@ -714,7 +714,6 @@ int retention_launch(const RetentionArgs& a, size_t smem, cudaStream_t stream) {
     const int r = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
     const size_t reg_smem = (size_t)RET_BATCH * (2 * slices * r + 2 * a.vdim + slices * a.vdim) * sizeof(float);
     if (reg_smem > 200 * 1024) continue;
-#define RET_THREADS_ARG(T) T
 #define K4(M) retention_reg_kernel<OT, M, 4, 256>
 #define K8(M) retention_reg_kernel<OT, M, 8, 256>
 #define K16(M) retention_reg_kernel<OT, M, 16, 256>
@@ -742,7 +741,6 @@ int retention_launch(const RetentionArgs& a, size_t smem, cudaStream_t stream) {
 #undef K8W
 #undef K16W
 #undef K32W
-#undef RET_THREADS_ARG
   }
 #define KS(M) retention_kernel<OT, M>
   RET_RUN(KS, smem, RET_THREADS);

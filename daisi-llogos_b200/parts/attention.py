@@ -138,7 +138,7 @@ class Attention(Mixer):
             self.sinks = as_f32(tensors["sink"], self.env)
         if self.blend_group is not None:
             self.v_lambda = as_f32(tensors["vmix"], self.env).reshape(1)
-        self.qkv_width = self.w_qkv.shape[0]
+        self.qkv_width = self.qkv_width_of() if self.own_kv else self.w_qkv.shape[0]
         if self.conv_taps:
             self.w_conv = torch.cat([as_f32(tensors[n + ".conv"], self.env) for n in names], dim=0).contiguous()
         if self.out_gate:
@@ -160,6 +160,7 @@ class Attention(Mixer):
         return kv
 
     def qkv_width_of(self) -> int:
+        """Columns of the q | k | v rows of a layer that projects its own keys and values."""
         return (self.nh + self.nkv) * self.hd + self.nkv * self.vd
 
     def check_borrowed(self, need) -> None:
@@ -218,8 +219,8 @@ class Attention(Mixer):
             else:
                 gate = linear(ctx, x, self.w_gate, "attn.gate", torch.float32)
         if self.conv_taps:
-            # the convolution sees the projections' float32 sums (times the row scale's factor: it is linear) and leaves
-            # one set of float32 rows of q | k | v for the preparation
+            # the convolution sees the projections' float32 sums and leaves one set of float32 rows of q | k | v for the
+            # preparation
             if row_scale is not None:
                 raise ValueError("attention: a convolution behind the projections takes finished rows (no row scale)")
             mixed = ctx.buffer("attn.conv", (1, n, self.qkv_width), torch.float32)
