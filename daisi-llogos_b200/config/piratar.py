@@ -136,8 +136,10 @@ class PiratarConfig:
         pair = None
         if em.get("bigram") is not None:
             bg = _obj(em, "bigram")
-            pair = PairHash(_positive(bg, "buckets", "embedding.bigram."), _int(bg, "mul_prev", "embedding.bigram."),
-                            _int(bg, "mul_cur", "embedding.bigram."))
+            buckets = _positive(bg, "buckets", "embedding.bigram.")
+            # only a multiplier's remainder matters; taking it here keeps the products small and not negative
+            pair = PairHash(buckets, _int(bg, "mul_prev", "embedding.bigram.", negative=True) % buckets,
+                            _int(bg, "mul_cur", "embedding.bigram.", negative=True) % buckets)
         side_dim = 0
         if d.get("token_side") is not None:
             side_dim = _positive(_obj(d, "token_side"), "dim", "token_side.")
@@ -149,12 +151,12 @@ class PiratarConfig:
                    embed_scale=scale, pair=pair, side_dim=side_dim, layers=layers)
 
 
-def _int(d: Mapping[str, Any], key: str, where: str) -> int:
+def _int(d: Mapping[str, Any], key: str, where: str, negative: bool = False) -> int:
     try:
         v = _need(d, key, int)
     except ConfigError as e:
         raise ConfigError(str(e).replace(f"'{key}'", f"'{where}{key}'")) from None
-    if v < 0:
+    if v < 0 and not negative:
         raise ConfigError(f"config.json: key '{where}{key}' must not be negative, got {v}")
     return v
 
